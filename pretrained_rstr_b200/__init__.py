@@ -69,7 +69,9 @@ def load_lm(path: str, opts: Optional[Dict] = None, *, gpu: bool = True,
         raise ValueError("pretrained_rstr_b200 has no CPU path: load_lm(..., gpu=True) only")
     from .config.registry import read_config
     _arch, config = read_config(path)
-    per_request = config.max_positions if maxpos is None else min(int(maxpos), config.max_positions)
+    from .engine.loading import DEFAULT_POSITIONS
+    per_request = min(config.max_positions, DEFAULT_POSITIONS) if maxpos is None \
+        else min(int(maxpos), config.max_positions)
     if max_tokens is None:
         max_tokens = max_lanes * (-(-per_request // page_size) * page_size)
     loaded = load_model(path, dtype=dtype, device=device_id, page_size=page_size,

@@ -58,6 +58,7 @@ class GroupSpec:
     kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    pools_per_layer: int = 2          # keys and values; 1: one row per token serves as both
 
     @property
     def elements_per_token(self) -> int:

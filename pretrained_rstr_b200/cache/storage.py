@@ -1,7 +1,8 @@
 """Device memory of the cache: pages per group and state slots.
 
 Pages of a group: one tensor ``[pools, pages, kv_heads, page_size, head_dim]`` with
-``pools = 2 * layers`` (keys of layer i at pool 2i, values at 2i+1), so one page id
+``pools = 2 * layers`` (keys of layer i at pool 2i, values at 2i+1; a group whose mixers keep
+one row per token as key and value has one pool per layer), so one page id
 addresses every layer of the group (``src/pretrained/continuation/page_pool.clj:4-6``)
 and a page of one (layer, head) is one contiguous tile.  Element type: the runtime's
 (bfloat16 when serving, float32 on the 32-bit path).
@@ -27,14 +28,16 @@ class CacheStorage:
         self.num_pages = list(num_pages)
         self.kv: List[torch.Tensor] = []
         for g, n in zip(self.groups, self.num_pages):
-            self.kv.append(torch.zeros((2 * len(g.layers), n, g.kv_heads, page_size, g.head_dim),
-                                       dtype=dtype, device=device))
+            self.kv.append(torch.zeros((g.pools_per_layer * len(g.layers), n, g.kv_heads, page_size,
+                                        g.head_dim), dtype=dtype, device=device))
         self.state: Dict[Tuple[int, str], torch.Tensor] = {
             key: torch.zeros((num_slots,) + tuple(spec.shape), dtype=spec.dtype, device=device)
             for key, spec in state_specs.items()}
 
     def layer_pages(self, group: int, index_in_group: int):
         kv = self.kv[group]
+        if self.groups[group].pools_per_layer == 1:
+            return kv[index_in_group], None
         return kv[2 * index_in_group], kv[2 * index_in_group + 1]
 
     def copy_pages(self, group: int, pairs: torch.Tensor, n_pairs: int, status) -> None:

@@ -46,6 +46,9 @@ class LayerSpec:
     ``norms`` are the layer's norms by the names its arrangement asks for: ``pre_norm``
     wants ``"mixer"`` and ``"feed_forward"``; a block with sandwich norms would name four,
     a parallel block one.  ``width`` is the width of the residual stream.
+    ``arrangement_params``: constants and tensor names of the arrangement itself (a scale of
+    the stream, gates of the branches); an arrangement that has some is built as
+    ``factory(mixer, feed_forward, norms, width, runtime, params=..., store=...)``.
     """
 
     prefix: str
@@ -54,6 +57,7 @@ class LayerSpec:
     feed_forward: PartSpec
     norms: Dict[str, PartSpec]
     width: int
+    arrangement_params: Dict[str, Any] = field(default_factory=dict)
 
 
 @dataclass(frozen=True)

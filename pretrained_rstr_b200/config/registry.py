@@ -37,7 +37,7 @@ class Architecture:
 
 
 _REGISTRY: Dict[str, Architecture] = {}
-_BUNDLED = ("pretrained_rstr_b200.models.gpt2",)
+_BUNDLED = ("pretrained_rstr_b200.models.gpt2", "pretrained_rstr_b200.models.redisun")
 _bundled_loaded = False
 
 
@@ -63,12 +63,15 @@ def _ensure_bundled() -> None:
 
 
 def dispatch_keys(raw: Dict[str, Any]) -> List[str]:
-    """Identifiers to try, in order: ``architectures[]`` entries, then ``model_type``."""
+    """Identifiers to try, in order: ``architectures[]`` entries, a single ``architecture``
+    name, then ``model_type``."""
     keys: List[str] = []
     archs = raw.get("architectures") or []
     if isinstance(archs, str):
         archs = [archs]
     keys.extend(str(a) for a in archs)
+    if isinstance(raw.get("architecture"), str):
+        keys.append(raw["architecture"])
     if raw.get("model_type"):
         keys.append(str(raw["model_type"]))
     return keys

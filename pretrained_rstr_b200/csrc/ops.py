@@ -132,6 +132,19 @@ def _declare(h: ctypes.CDLL) -> None:
     h.prb_sample_max_top_k.argtypes = []
     h.prb_sample_workspace_words.argtypes = []
     h.prb_sample_workspace_words.restype = c_int
+    h.prb_embed_pair.argtypes = [P, P, P, P, P, P, P, P, P, I, I, I, L, L, L, I, I, I, P, P]
+    h.prb_rms_norm.argtypes = [P, P, P, P, P, L, P, P, P, P, I, I, I, F, F, I, P, P]
+    h.prb_gated_pair.argtypes = [P, L, I, P, L, I, I, I, I, F, F, F, P, L, I, I, P]
+    h.prb_route.argtypes = [P, P, P, P, L, P, P, I, I, I, I, I, P]
+    h.prb_latent_prepare.argtypes = [P, L, P, P, L, I, I, P, P, P, P, P, I, I, I, I, I, I, I, F,
+                                     I, I, P, P]
+    h.prb_latent_fold.argtypes = [P, P, L, P, P, P, I, I, I, I, I, I, I, P]
+    h.prb_latent_attention.argtypes = [P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, I, P, P]
+    h.prb_latent_unfold.argtypes = [P, L, P, P, P, L, I, I, I, I, I, I, P]
+    for name in ("prb_embed_pair", "prb_rms_norm", "prb_gated_pair", "prb_route",
+                 "prb_latent_prepare", "prb_latent_fold", "prb_latent_attention",
+                 "prb_latent_unfold"):
+        getattr(h, name).restype = c_int
     for name in ("prb_resolve_tokens", "prb_fetch_step", "prb_publish_result", "prb_embed", "prb_layernorm", "prb_bias_act", "prb_kv_append", "prb_copy_pages",
                  "prb_gemm_f32", "prb_gemm_bf16", "prb_gemm_bf16_scatter", "prb_gemm_midm",
                  "prb_gemm_midm_supports", "prb_gemm_smallm", "prb_gemm_smallm_max_rows",
@@ -788,3 +801,215 @@ def sample(out, logits, n_rows, temperature=None, top_k=None, top_p=None, seeds=
                             _p(temperature), _p(top_k), _p(top_p), _p(seeds), _p(fresh), _p(slots),
                             _p(rng_states), n_rows, *pub, _p(workspace), _stream()), what)
 
+
+
+# ------------------------------------------- gated branches, norms after the sum, routers
+def embed_pair(out, tokens, positions, seq_of_token, q_start, state_slot, prev_state, table,
+               pairs, buckets: int, mul_prev: int, mul_cur: int, status) -> None:
+    """out[t,:] = table[tokens[t],:] + pairs[row,:] with row = (prev * mul_prev + token *
+    mul_cur) mod buckets, or row ``buckets`` for a sequence's first token; out float32
+    [T, width].  ``prev_state`` (int32 [slots]) holds every request's last token between
+    steps and is brought up to date by this call."""
+    what = "embed_pair"
+    _need(out, torch.float32, "out", what)
+    for name, t in (("tokens", tokens), ("positions", positions), ("seq_of_token", seq_of_token),
+                    ("q_start", q_start), ("state_slot", state_slot), ("prev_state", prev_state)):
+        _need(t, torch.int32, name, what)
+    _need(table, None, "table", what)
+    _need(pairs, table.dtype, "pairs", what)
+    n, width = out.shape
+    buckets = int(buckets)
+    if table.shape[1] != width or pairs.shape[1] != width or pairs.shape[0] != buckets + 1:
+        raise KernelArgumentError(f"{what}: table widths differ from the output's, or the pair "
+                                  f"table has not buckets + 1 rows")
+    if min(tokens.numel(), positions.numel(), seq_of_token.numel()) < n:
+        raise KernelArgumentError(f"{what}: fewer token ids, positions or requests than output rows")
+    _check(lib().prb_embed_pair(_p(out), _p(tokens), _p(positions), _p(seq_of_token), _p(q_start),
+                                _p(state_slot), _p(prev_state), _p(table), _p(pairs), n, width,
+                                table.shape[0], buckets, int(mul_prev) % buckets,
+                                int(mul_cur) % buckets, prev_state.numel(), state_slot.numel(),
+                                dtype_code(table.dtype), _p(status), _stream()), what)
+
+
+def rms_norm(x, out=None, x_out=None, y=None, gate=None, gate_bias=None, gain=None, weight=None,
+             rows=None, alpha: float = 1.0, eps: float = 0.0, status=None) -> None:
+    """v = alpha * x (+ y, or + sigmoid(gate + gate_bias) * y); r = v / sqrt(mean(v^2) + eps)
+    * gain (one number on the device) * weight (per coordinate).  r goes to ``out`` (float32 or
+    bfloat16) and/or ``x_out`` (float32; may be ``x`` itself); with ``rows`` row i of the result
+    comes from row rows[i] of the inputs.  ``gate`` may be a column slice of a wider tensor."""
+    what = "rms_norm"
+    _need(x, torch.float32, "x", what)
+    width = x.shape[1]
+    n_rows = (out if out is not None else x_out).shape[0]
+    for name, t in (("out", out), ("x_out", x_out)):
+        if t is not None:
+            _need(t, None if name == "out" else torch.float32, name, what)
+            if t.shape[1] != width or t.shape[0] != n_rows:
+                raise KernelArgumentError(f"{what}: {name} has the wrong shape")
+    if y is not None:
+        _need(y, torch.float32, "y", what)
+        if y.shape != x.shape:
+            raise KernelArgumentError(f"{what}: y must have x's shape")
+    gate_ld = 0
+    if gate is not None:
+        if y is None or gate.dtype != torch.float32 or gate.stride(1) != 1 or \
+                gate.shape[1] != width or gate.shape[0] < x.shape[0]:
+            raise KernelArgumentError(f"{what}: gate must be float32 [rows, width] beside a branch y")
+        gate_ld = gate.stride(0)
+    for name, t, size in (("gate_bias", gate_bias, width), ("gain", gain, 1), ("weight", weight, width)):
+        if t is not None:
+            _need(t, torch.float32, name, what)
+            if t.numel() != size:
+                raise KernelArgumentError(f"{what}: {name} must hold {size} numbers")
+    if rows is not None:
+        _need(rows, torch.int32, "rows", what)
+    elif x.shape[0] < n_rows:
+        raise KernelArgumentError(f"{what}: fewer input rows than output rows")
+    _check(lib().prb_rms_norm(_p(out), _p(x_out), _p(x), _p(y), _p(gate), gate_ld, _p(gate_bias),
+                              _p(gain), _p(weight), _p(rows), n_rows, x.shape[0], width,
+                              float(alpha), float(eps),
+                              dtype_code(out.dtype) if out is not None else F32, _p(status),
+                              _stream()), what)
+
+
+def gated_pair(out, inp, gate_col: int, up_col: int, n: int, out_col: int = 0, limit: float = 0.0,
+               act_alpha: float = 1.0, up_shift: float = 0.0, scale=None, group: int = 1) -> None:
+    """out[t, out_col + i] = g * sigmoid(act_alpha * g) * (u + up_shift) (* scale[t, i // group])
+    for i < n, with g = inp[t, gate_col + i] and u = inp[t, up_col + i] (float32), g capped at
+    ``limit`` and u clamped to +-``limit`` when ``limit`` > 0."""
+    what = "gated_pair"
+    if not inp.is_cuda or inp.dtype != torch.float32 or inp.stride(1) != 1:
+        raise KernelArgumentError(f"{what}: inp must be float32 on CUDA with unit inner stride")
+    if not out.is_cuda or out.stride(1) != 1 or out.shape[0] < inp.shape[0] or \
+            out_col + n > out.shape[1] or max(gate_col, up_col) + n > inp.shape[1]:
+        raise KernelArgumentError(f"{what}: columns outside the tensors")
+    if scale is not None:
+        if scale.dtype != torch.float32 or scale.stride(1) != 1 or scale.shape[0] < inp.shape[0] \
+                or scale.shape[1] * group < n:
+            raise KernelArgumentError(f"{what}: scale must be float32 [rows, ceil(n / group)]")
+    _check(lib().prb_gated_pair(_p(out), out.stride(0), int(out_col), _p(inp), inp.stride(0),
+                                int(gate_col), int(up_col), int(n), inp.shape[0], float(limit),
+                                float(act_alpha), float(up_shift), _p(scale),
+                                0 if scale is None else scale.stride(0), int(group),
+                                dtype_code(out.dtype), _stream()), what)
+
+
+def route(scale, chosen, chosen_w, x, w, bias, top: int) -> None:
+    """Router: z = x . w^T + bias in 32-bit (x float32 [T, width]; w [experts, width]), or,
+    with ``w`` None, z = x + bias (x float32 [T, experts]: logits a product has made, possibly a
+    column slice of a wider tensor); the ``top`` largest per row and the softmax over them.
+    scale float32 [T, experts] (zero where not chosen), chosen int32 [T, top], chosen_w
+    float32 [T, top]."""
+    what = "route"
+    if not x.is_cuda or x.dtype != torch.float32 or x.stride(1) != 1:
+        raise KernelArgumentError(f"{what}: x must be float32 on CUDA with unit inner stride")
+    _need(scale, torch.float32, "scale", what)
+    _need(chosen, torch.int32, "chosen", what)
+    _need(chosen_w, torch.float32, "chosen_w", what)
+    n, width = x.shape
+    experts = width if w is None else w.shape[0]
+    if w is not None:
+        _need(w, None, "w", what)
+        if w.shape[1] != width:
+            raise KernelArgumentError(f"{what}: shapes do not fit")
+    if scale.shape != (n, experts) or chosen.shape != (n, top) or chosen_w.shape != (n, top):
+        raise KernelArgumentError(f"{what}: shapes do not fit")
+    if bias is not None:
+        _need(bias, torch.float32, "bias", what)
+    _check(lib().prb_route(_p(scale), _p(chosen), _p(chosen_w), _p(x), x.stride(0), _p(w), _p(bias),
+                           n, width, experts, int(top), F32 if w is None else dtype_code(w.dtype),
+                           _stream()), what)
+
+
+# ----------------------------------------------------- attention over a shared latent
+def latent_prepare(cq, cache, proj, q_col: int, kv_col: int, wq, wkv, slots, positions, freq,
+                   q_rank: int, rank: int, rot_dim: int, rot_dims: int, eps: float, status) -> None:
+    """Per token: the query latent proj[t, q_col : q_col + q_rank], unit-RMS-normed with weight
+    ``wq``, goes to ``cq`` ([T, >= q_rank], activation type); the key/value latent
+    proj[t, kv_col : kv_col + rank], normed with ``wkv``, and the ``rot_dim`` columns after it,
+    rotated by the token's position, go to the token's cache row (``cache``: [pages, 1,
+    page size, rank + rot_dim]).  ``proj`` is float32 and may be a wider row-major tensor."""
+    what = "latent_prepare"
+    if proj.dtype != torch.float32 or proj.stride(1) != 1:
+        raise KernelArgumentError(f"{what}: proj must be float32 with unit inner stride")
+    _need(cache, None, "cache", what)
+    num_pages, kv_heads, page_size, row = cache.shape
+    if kv_heads != 1 or row != rank + rot_dim:
+        raise KernelArgumentError(f"{what}: the cache must be [pages, 1, page size, {rank + rot_dim}]")
+    if cq.stride(1) != 1 or cq.shape[1] < q_rank or cq.shape[0] < proj.shape[0]:
+        raise KernelArgumentError(f"{what}: cq has the wrong shape")
+    for name, t in (("wq", wq), ("wkv", wkv), ("freq", freq)):
+        _need(t, torch.float32, name, what)
+    if wq.numel() != q_rank or wkv.numel() != rank or freq.numel() < rot_dims // 2 or \
+            max(q_col + q_rank, kv_col + rank + rot_dim) > proj.shape[1]:
+        raise KernelArgumentError(f"{what}: weights or columns do not fit")
+    if slots is not None:
+        _need(slots, torch.int32, "slots", what)
+    _need(positions, torch.int32, "positions", what)
+    _check(lib().prb_latent_prepare(_p(cq), cq.stride(0), _p(cache), _p(proj), proj.stride(0),
+                                    int(q_col), int(kv_col), _p(wq), _p(wkv), _p(slots),
+                                    _p(positions), _p(freq), proj.shape[0], q_rank, rank, rot_dim,
+                                    rot_dims, page_size, num_pages, float(eps),
+                                    dtype_code(cache.dtype), dtype_code(cq.dtype), _p(status),
+                                    _stream()), what)
+
+
+def latent_fold(qa, q, uk, positions, freq, heads: int, dim: int, rot_dim: int, rot_dims: int,
+                rank: int) -> None:
+    """qa[t, h, :rank] = Uk_h^T q[t, h, :dim]; qa[t, h, rank:] = q[t, h, dim:] rotated by the
+    token's position.  q float32 [T, heads * (dim + rot_dim)]; uk [heads * dim, rank];
+    qa float32 [T, heads, rank + rot_dim]."""
+    what = "latent_fold"
+    if q.dtype != torch.float32 or q.stride(1) != 1 or q.shape[1] != heads * (dim + rot_dim):
+        raise KernelArgumentError(f"{what}: q must be float32 [T, heads * (dim + rot_dim)]")
+    _need(qa, torch.float32, "qa", what)
+    _need(uk, None, "uk", what)
+    if tuple(uk.shape) != (heads * dim, rank) or tuple(qa.shape) != (q.shape[0], heads, rank + rot_dim):
+        raise KernelArgumentError(f"{what}: shapes do not fit")
+    _check(lib().prb_latent_fold(_p(qa), _p(q), q.stride(0), _p(uk), _p(positions), _p(freq),
+                                 q.shape[0], heads, dim, rot_dim, rot_dims, rank,
+                                 dtype_code(uk.dtype), _stream()), what)
+
+
+def latent_attention(out, qa, cache, block_table, seq_of_token, positions, sinks, scale: float,
+                     window, rank: int, status) -> None:
+    """out[t, h, :] = sum_j w_j c_j over the keys token t sees, w = softmax of
+    scale * qa[t, h] . [c_j | r_j] whose denominator also holds exp(sinks[h]) when ``sinks`` is
+    given.  32-bit arithmetic, any sizes (rank up to 1,024)."""
+    what = "latent_attention"
+    _need(out, torch.float32, "out", what)
+    _need(qa, torch.float32, "qa", what)
+    _need(cache, None, "cache", what)
+    num_pages, kv_heads, page_size, row = cache.shape
+    n, heads, d = qa.shape
+    if kv_heads != 1 or row != d or tuple(out.shape) != (n, heads, rank) or rank > d:
+        raise KernelArgumentError(f"{what}: shapes do not fit")
+    if sinks is not None:
+        _need(sinks, torch.float32, "sinks", what)
+        if sinks.numel() != heads:
+            raise KernelArgumentError(f"{what}: one sink per head")
+    _need(block_table, torch.int32, "block_table", what)
+    _check(lib().prb_latent_attention(_p(out), _p(qa), _p(cache), _p(block_table),
+                                      _p(seq_of_token), _p(positions), _p(sinks), n, heads, rank,
+                                      d - rank, page_size, block_table.shape[1], num_pages,
+                                      float(scale), int(window or 0), dtype_code(cache.dtype),
+                                      _p(status), _stream()), what)
+
+
+def latent_unfold(out, lat, uvt, gate, heads: int, rank: int, vdim: int) -> None:
+    """out[t, h*vdim + v] = sigmoid(gate[t, h]) * sum_r uvt[h, r, v] * lat[t, h, r]; ``gate``
+    float32 [T, heads] (may be a column slice) or None."""
+    what = "latent_unfold"
+    _need(lat, torch.float32, "lat", what)
+    _need(uvt, None, "uvt", what)
+    if tuple(uvt.shape) != (heads, rank, vdim) or tuple(lat.shape[1:]) != (heads, rank) or \
+            out.stride(1) != 1 or out.shape[1] != heads * vdim or out.shape[0] < lat.shape[0]:
+        raise KernelArgumentError(f"{what}: shapes do not fit")
+    gate_ld = 0
+    if gate is not None:
+        if gate.dtype != torch.float32 or gate.stride(1) != 1 or gate.shape[1] != heads:
+            raise KernelArgumentError(f"{what}: gate must be float32 [T, heads]")
+        gate_ld = gate.stride(0)
+    _check(lib().prb_latent_unfold(_p(out), out.stride(0), _p(lat), _p(uvt), _p(gate), gate_ld,
+                                   lat.shape[0], heads, rank, vdim, dtype_code(uvt.dtype),
+                                   dtype_code(out.dtype), _stream()), what)

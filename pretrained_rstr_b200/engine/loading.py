@@ -20,6 +20,10 @@ from ..weights.loader import load_weights
 from .batch import Runtime
 from .runner import ModelRunner
 
+#: positions a request may hold when neither the caller nor the design says (a design that names
+#: no limit is otherwise served up to what its page pool holds)
+DEFAULT_POSITIONS = 8192
+
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16,
            "float32": torch.float32, "fp32": torch.float32, "f32": torch.float32}
 
@@ -86,15 +90,20 @@ def load_model(folder: str, dtype="bfloat16", device="cuda:0", page_size: int = 
     store.release()
     if num_pages is None:
         if max_tokens is None:
-            max_tokens = max_requests * (-(-config.max_positions // page_size) * page_size)
+            per_request = min(config.max_positions, DEFAULT_POSITIONS)
+            max_tokens = max_requests * (-(-per_request // page_size) * page_size)
         num_pages = max(1, -(-max_tokens // page_size))
     pages = [num_pages] * len(model.group_specs)
+    # A request never holds more than the pool does: a design without a position limit of its
+    # own (or with a larger one) is served up to that.
+    positions = min(config.max_positions, num_pages * page_size)
+    model.max_positions = positions
     storage = CacheStorage(model.group_specs, pages, page_size, dtype, device,
                            model.state_specs, max_requests)
     # A model whose parts keep state of fixed size per request cannot skip shared prompt
     # tokens (their state updates would never run), and a fork has to copy the state rows.
     cache = CacheManager(model.group_specs, page_size, pages if pages else 1, max_requests,
-                         config.max_positions, share_prefixes=share_prefixes,
+                         positions, share_prefixes=share_prefixes,
                          has_state=bool(model.state_specs), copy_state=storage.copy_state)
     runner = ModelRunner(model, runtime, cache, storage)
     return LoadedModel(folder, arch, config, runtime, model, cache, storage, runner)

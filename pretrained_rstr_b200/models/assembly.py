@@ -33,6 +33,9 @@ class Model:
         self.final_norm, self.head = final_norm, head
         self.width, self.vocab = width, vocab
         self.max_positions = config.max_positions
+        #: optional ``tap(run index, x)`` called after every block (measurements and tests; a
+        #: model with a tap is not replayed from CUDA graphs)
+        self.tap = None
         # cache layout
         self.group_specs: List[GroupSpec] = []
         self.layer_group: Dict[int, Tuple[int, int]] = {}     # cache layer -> (group, index)
@@ -67,22 +70,26 @@ class Model:
             mixer = self.blocks[layer].mixer
             spec = mixer.kv_spec()
             if spec is not None:
-                keyed.setdefault((spec.kv_heads, spec.head_dim, spec.window), []).append(layer)
+                keyed.setdefault((spec.kv_heads, spec.head_dim, spec.window,
+                                  2 if spec.values else 1), []).append(layer)
             for st in mixer.state_specs():
                 self.state_specs[(layer, st.name)] = st
-        for (kv_heads, head_dim, window), layers in sorted(
+        for st in self.embedding.state_specs() if hasattr(self.embedding, "state_specs") else ():
+            self.state_specs[(-1, st.name)] = st            # (-1: the embedding's own state)
+        for (kv_heads, head_dim, window, pools), layers in sorted(
                 keyed.items(), key=lambda kv: kv[1][0]):
             name = "full" if window is None else f"window{window}"
             gi = len(self.group_specs)
             self.group_specs.append(GroupSpec(f"{name}.{gi}", tuple(layers), kv_heads, head_dim,
-                                              window))
+                                              window, pools))
             for idx, layer in enumerate(layers):
                 self.layer_group[layer] = (gi, idx)
         for e in self.order:
             reader = self.blocks[e.layer].mixer.kv_spec()
             if reader is not None and e.cache_layer in self.layer_group:
                 g = self.group_specs[self.layer_group[e.cache_layer][0]]
-                if (reader.kv_heads, reader.head_dim) != (g.kv_heads, g.head_dim):
+                if (reader.kv_heads, reader.head_dim, 2 if reader.values else 1) != \
+                        (g.kv_heads, g.head_dim, g.pools_per_layer):
                     raise ValueError(f"run order: layer {e.layer} cannot read the cache of layer "
                                      f"{e.cache_layer}: head counts or sizes differ")
 
@@ -98,6 +105,9 @@ class Model:
             cache.state = {name: t for (layer, name), t in storage.state.items()
                            if layer == e.cache_layer}
             self._caches.append(cache)
+        own = {name: t for (layer, name), t in storage.state.items() if layer == -1}
+        if own:
+            self.embedding.bind_state(own)
 
     # --------------------------------------------------------------------- forward
     def forward(self, ctx) -> torch.Tensor:
@@ -108,7 +118,12 @@ class Model:
         x = ctx.scratch("residual", (ctx.token_capacity, self.width), torch.float32)[:t]
         self.embedding.forward(ctx, self.position, x)
         for entry, cache in zip(self.order, self._caches):
-            self.blocks[entry.layer].forward(ctx, x, cache)
+            block = self.blocks[entry.layer]
+            block.forward(ctx, x, cache)
+            ctx.last_block = block             # (a block may leave something for its successor)
+            if self.tap is not None:
+                self.tap(len(getattr(ctx, "_tapped", [])), x)
+                ctx._tapped = getattr(ctx, "_tapped", []) + [entry.layer]
         r = ctx.launch_rows
         if r == 0:
             return torch.empty((0, self.vocab), dtype=torch.float32, device=x.device)
@@ -134,8 +149,12 @@ def build_model(config, store, runtime) -> Model:
         mixer = build_part("mixer", spec.mixer, store, runtime)
         ff = build_part("feed_forward", spec.feed_forward, store, runtime)
         norms = {name: build_part("norm", ns, store, runtime) for name, ns in spec.norms.items()}
-        blocks.append(part_factory("arrangement", spec.arrangement)(mixer, ff, norms, spec.width,
-                                                                    runtime))
+        factory = part_factory("arrangement", spec.arrangement)
+        if spec.arrangement_params:
+            blocks.append(factory(mixer, ff, norms, spec.width, runtime,
+                                  params=spec.arrangement_params, store=store))
+        else:
+            blocks.append(factory(mixer, ff, norms, spec.width, runtime))
     position = build_part("position", config.position_spec(), store, runtime)
     for block in blocks:                      # rotary-style encodings act inside the mixer
         if hasattr(block.mixer, "position") and block.mixer.position is None:

@@ -1,4 +1,4 @@
-from . import attention, block, embedding, feed_forward, head, norms, positions  # noqa: F401  (register)
+from . import attention, block, embedding, feed_forward, head, latent_attention, norms, positions  # noqa: F401  (register)
 from .interfaces import (Block, Embedding, FeedForward, Head, KVSpec, LayerCache, Mixer, Norm,
                          PositionEncoding, StateSpec)
 from .linear import Linear

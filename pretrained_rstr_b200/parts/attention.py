@@ -160,6 +160,7 @@ class AttentionWork(WorkPlanner):
 class CausalAttention(Mixer):
     graph_safe = True
     accepts_lazy_norm = True      # the first matrix product may compute the norm itself
+    can_overwrite = True
     def __init__(self, qkv: Linear, out: Linear, width: int, n_head: int, n_kv_head: int,
                  head_dim: int, scale: float, window: Optional[int], runtime,
                  position=None):
@@ -186,7 +187,7 @@ class CausalAttention(Mixer):
     def work_planners(self):
         return [self.work_plan]
 
-    def forward(self, ctx, h, x, cache: LayerCache) -> None:
+    def forward(self, ctx, h, x, cache: LayerCache, accumulate: bool = True) -> None:
         t = x.shape[0]
         dtype = self.runtime.dtype
         qkv = ctx.scratch("attn_qkv", (ctx.token_capacity, self.qkv.n_out), dtype)[:t]
@@ -217,7 +218,7 @@ class CausalAttention(Mixer):
         # on the SMs and the pair lasts longer (measured, a layer of GPT-2 small: 30.3 -> 29.5
         # us at 8 requests, 25.5 -> 24.1 us at one).
         with ops.plain_launch(last == "split"):
-            self.out.forward(ctx, o, x, resid=x)
+            self.out.forward(ctx, o, x, resid=x if accumulate else None)
 
 
 def prefill_key_parts(items: int, max_context: int, window: Optional[int]):

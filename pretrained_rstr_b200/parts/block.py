@@ -5,8 +5,11 @@ from __future__ import annotations
 
 from typing import Dict
 
+import torch
+
+from ..csrc import ops
 from .interfaces import Block, FeedForward, LayerCache, Mixer, Norm
-from .linear import LazyNorm
+from .linear import LazyNorm, Linear
 from .registry import register_part
 
 
@@ -38,4 +41,81 @@ class PreNormBlock(Block):
         return lazy if getattr(consumer, "accepts_lazy_norm", False) else lazy.tensor()
 
 
+class PostNormGatedBlock(Block):
+    """x <- norm_1(alpha x + g_1(x) * mixer(x)); x <- norm_2(alpha x + g_2(x) * feed_forward(x)):
+    the branches read the stream itself, the norm comes after the sum, and a branch's result may
+    be gated element by element by g(x) = sigmoid(W x + b) (``params["gates"]``: branch name ->
+    tensor name of W, with ``.b``).  A layer without a feed-forward has the first half only.
+
+    The gate's matrix rides along in the branch's first matrix product where the part offers
+    that (``fuse_input_rows``); sum, gate and norm are one kernel, which also leaves the
+    stream's copy in the activation type for the next branch's product."""
+    graph_safe = True
+
+    def __init__(self, mixer: Mixer, feed_forward: FeedForward, norms: Dict[str, Norm],
+                 width: int, runtime, params=None, store=None):
+        params = params or {}
+        self.mixer, self.feed_forward = mixer, feed_forward
+        self.norms = dict(norms)
+        self.width, self.runtime = width, runtime
+        self.alpha = float(params.get("alpha", 1.0))
+        self.has_ff = not getattr(feed_forward, "is_none", False)
+        wanted = {"mixer"} | ({"feed_forward"} if self.has_ff else set())
+        if set(norms) != wanted:
+            raise ValueError(f"post_norm_gated wants the norms {sorted(wanted)}, got {sorted(norms)}")
+        for part in (mixer, feed_forward):
+            if not getattr(part, "can_overwrite", False):
+                raise ValueError(f"post_norm_gated: {type(part).__name__} cannot hand over its "
+                                 f"result apart from the stream")
+        for norm in norms.values():
+            if not hasattr(norm, "joined"):
+                raise ValueError("post_norm_gated needs norms that can join a branch to the stream")
+        self.gates = {}
+        for name, tensor in (params.get("gates") or {}).items():
+            part = {"mixer": mixer, "feed_forward": feed_forward}[name]
+            w, b = store.get(tensor), store.get(tensor + ".b")
+            if tuple(w.shape) != (width, width) or b.numel() != width:
+                raise ValueError(f"{tensor}: a gate of the stream is [{width}, {width}] with a bias")
+            bias = b.to(torch.float32).contiguous()
+            if hasattr(part, "fuse_input_rows"):
+                self.gates[name] = (part.fuse_input_rows("branch_gate", w), None, bias)
+            else:
+                self.gates[name] = (None, Linear(w, None, runtime), bias)
+
+    def forward(self, ctx, x, cache: LayerCache) -> None:
+        t = x.shape[0]
+        cap = ctx.token_capacity
+        y = ctx.scratch("branch_result", (cap, self.width), torch.float32)[:t]
+        serving = self.runtime.dtype != torch.float32
+        copy = ctx.scratch("stream_copy", (cap, self.width), self.runtime.dtype)[:t] if serving else None
+        # the stream in the products' type: the norm before left it, unless this is the model's
+        # first branch or another kind of block has changed the stream since
+        writer = getattr(ctx, "stream_copy_by", None)
+        current = writer is not None and writer is getattr(ctx, "last_block", None)
+        for name, part in (("mixer", self.mixer), ("feed_forward", self.feed_forward)):
+            if name == "feed_forward" and not self.has_ff:
+                break
+            h = x
+            if serving:
+                if not current:
+                    ops.bias_act(copy, x, None, None, None)
+                h = copy
+            if name == "mixer":
+                part.forward(ctx, h, y, cache, accumulate=False)
+            else:
+                part.forward(ctx, h, y, accumulate=False)
+            gate = bias = None
+            if name in self.gates:
+                fused, own, bias = self.gates[name]
+                if fused is not None:
+                    gate = part.fused_rows(fused)
+                else:
+                    gate = ctx.scratch("branch_gate", (cap, self.width), torch.float32)[:t]
+                    own.forward(ctx, h, gate)
+            self.norms[name].joined(ctx, x, y, self.alpha, gate=gate, gate_bias=bias, copy=copy)
+            current = True
+        ctx.stream_copy_by = self
+
+
 register_part("arrangement", "pre_norm", PreNormBlock)
+register_part("arrangement", "post_norm_gated", PostNormGatedBlock)

@@ -3,6 +3,8 @@
 ``gpt2.clj:150``), activation and biases are parameters."""
 from __future__ import annotations
 
+import torch
+
 from ..csrc import ops
 from .interfaces import FeedForward
 from .linear import Linear
@@ -12,6 +14,7 @@ from .registry import register_part
 class DenseMLP(FeedForward):
     graph_safe = True
     accepts_lazy_norm = True      # the first matrix product may compute the norm itself
+    can_overwrite = True
     def __init__(self, up: Linear, down: Linear, width: int, inner: int, activation: str, runtime):
         if activation not in ops.ACT_CODES:
             raise ValueError(f"dense_mlp: unknown activation {activation!r}")
@@ -21,11 +24,11 @@ class DenseMLP(FeedForward):
         self.width, self.inner, self.activation = width, inner, activation
         self.runtime = runtime
 
-    def forward(self, ctx, h, x) -> None:
+    def forward(self, ctx, h, x, accumulate: bool = True) -> None:
         t = x.shape[0]
         u = ctx.scratch("mlp_inner", (ctx.token_capacity, self.inner), self.runtime.dtype)[:t]
         self.up.forward(ctx, h, u, act=self.activation)
-        self.down.forward(ctx, u, x, resid=x)
+        self.down.forward(ctx, u, x, resid=x if accumulate else None)
 
 
 def _dense_mlp(p, store, rt) -> DenseMLP:
@@ -37,4 +40,134 @@ def _dense_mlp(p, store, rt) -> DenseMLP:
     return DenseMLP(up, down, p["width"], p["inner"], p["activation"], rt)
 
 
+class NoFeedForward(FeedForward):
+    """A layer without a feed-forward (``is_none``: arrangements skip the branch)."""
+    graph_safe = True
+    can_overwrite = True
+    is_none = True
+
+    def forward(self, ctx, h, x, accumulate: bool = True) -> None:
+        if not accumulate:
+            x.zero_()
+
+
+class GatedMLP(FeedForward):
+    """down(f(gate(h)) * (up(h) + up_shift)) with f(g) = g * sigmoid(act_alpha * g); with
+    ``limit`` > 0 the gate's result is capped at ``limit`` and up's clamped to +-``limit``
+    first.  (act_alpha 1, shift 0, no limit: the usual SiLU-gated feed-forward.)  Gate and up
+    are one matrix product, in which rows of an arrangement may ride along
+    (:meth:`fuse_input_rows`); its float32 result feeds the activation unrounded."""
+    graph_safe = True
+    can_overwrite = True
+
+    def __init__(self, gate, up, down, width: int, inner: int, limit: float, act_alpha: float,
+                 up_shift: float, runtime):
+        from .latent_attention import FusedInput
+        for name, t, shape in (("gate", gate, (inner, width)), ("up", up, (inner, width)),
+                               ("down", down, (width, inner))):
+            if tuple(t.shape) != shape:
+                raise ValueError(f"gated_mlp: {name} is {list(t.shape)}, expected {list(shape)}")
+        self.input = FusedInput(width, runtime, "gated_in")
+        self.input.add("gate", gate)
+        self.input.add("up", up)
+        self.down = Linear(down, None, runtime)
+        self.width, self.inner = width, inner
+        self.limit, self.act_alpha, self.up_shift = float(limit), float(act_alpha), float(up_shift)
+        self.runtime = runtime
+
+    def fuse_input_rows(self, name: str, weight) -> str:
+        return self.input.add(name, weight)
+
+    def fused_rows(self, name: str):
+        return self.input.view(self._proj, name)
+
+    def forward(self, ctx, h, x, accumulate: bool = True) -> None:
+        t = x.shape[0]
+        proj = self._proj = self.input.run(ctx, h)
+        cols = self.input.cols
+        a = ctx.scratch("gated_act", (ctx.token_capacity, self.inner), self.runtime.dtype)[:t]
+        ops.gated_pair(a, proj, cols["gate"][0], cols["up"][0], self.inner, limit=self.limit,
+                       act_alpha=self.act_alpha, up_shift=self.up_shift)
+        self.down.forward(ctx, a, x, resid=x if accumulate else None)
+
+
+class GatedMoE(FeedForward):
+    """A router chooses ``top`` of ``experts`` gated feed-forwards per token (logits in
+    32-bit accumulators plus a bias; weights = softmax over the chosen logits alone); an
+    optional shared expert runs for every token.
+
+    All experts' gate and up rows, the shared expert's, the router's and whatever an
+    arrangement fuses in are ONE matrix product; the activations of experts a token did not
+    choose are multiplied by zero and those it chose by their weight, and one product with all
+    down matrices side by side sums the chosen experts (zeros add nothing).  Every token thus
+    pays for every expert's arithmetic: right for any sizes, cheap while experts are small."""
+    graph_safe = True
+    can_overwrite = True
+
+    def __init__(self, p: dict, store, runtime):
+        from .latent_attention import FusedInput
+        width, n, inner = p["width"], p["experts"], p["inner"]
+        self.width, self.experts, self.top, self.inner = width, n, p["top"], inner
+        self.shared_inner = int(p.get("shared_inner") or 0)
+        self.limit, self.shared_limit = float(p["limit"]), float(p.get("shared_limit") or 0.0)
+        self.act_alpha, self.up_shift = float(p["act_alpha"]), float(p["up_shift"])
+        self.runtime = runtime
+        pre = p["prefix"]
+
+        def need(name, shape):
+            t = store.get(pre + name)
+            if tuple(t.shape) != tuple(shape):
+                raise ValueError(f"{pre + name}: expected {list(shape)}, found {list(t.shape)}")
+            return t
+
+        self.input = FusedInput(width, runtime, "moe_in")
+        self.input.add("gate", torch.cat([need(f"e{e}.gate", (inner, width)) for e in range(n)]))
+        self.input.add("up", torch.cat([need(f"e{e}.up", (inner, width)) for e in range(n)]))
+        downs = [need(f"e{e}.down", (width, inner)) for e in range(n)]
+        if self.shared_inner:
+            self.input.add("shared_gate", need("shared.gate", (self.shared_inner, width)))
+            self.input.add("shared_up", need("shared.up", (self.shared_inner, width)))
+            downs.append(need("shared.down", (width, self.shared_inner)))
+        self.input.add("router", need("router", (n, width)))
+        self.router_bias = need("router.b", (n,)).to(torch.float32).contiguous()
+        self.down = Linear(torch.cat(downs, dim=1), None, runtime)
+
+    def fuse_input_rows(self, name: str, weight) -> str:
+        return self.input.add(name, weight)
+
+    def fused_rows(self, name: str):
+        return self.input.view(self._proj, name)
+
+    def forward(self, ctx, h, x, accumulate: bool = True) -> None:
+        t = x.shape[0]
+        cap = ctx.token_capacity
+        proj = self._proj = self.input.run(ctx, h)
+        cols = self.input.cols
+        scale = ctx.scratch("moe_scale", (cap, self.experts), torch.float32)[:t]
+        chosen = ctx.scratch("moe_chosen", (cap, self.top), torch.int32)[:t]
+        chosen_w = ctx.scratch("moe_chosen_w", (cap, self.top), torch.float32)[:t]
+        ops.route(scale, chosen, chosen_w, self.input.view(proj, "router"), None, self.router_bias,
+                  self.top)
+        n_act = self.experts * self.inner
+        a = ctx.scratch("moe_act", (cap, n_act + self.shared_inner), self.runtime.dtype)[:t]
+        ops.gated_pair(a, proj, cols["gate"][0], cols["up"][0], n_act, limit=self.limit,
+                       act_alpha=self.act_alpha, up_shift=self.up_shift, scale=scale,
+                       group=self.inner)
+        if self.shared_inner:
+            ops.gated_pair(a, proj, cols["shared_gate"][0], cols["shared_up"][0],
+                           self.shared_inner, out_col=n_act, limit=self.shared_limit,
+                           act_alpha=self.act_alpha, up_shift=self.up_shift)
+        self.down.forward(ctx, a, x, resid=x if accumulate else None)
+
+
+def _gated_mlp(p, store, rt) -> GatedMLP:
+    w = p["weights"]
+    return GatedMLP(store.get(w["gate"]), store.get(w["up"]), store.get(w["down"]), p["width"],
+                    p["inner"], p.get("limit", 0.0), p.get("act_alpha", 1.0),
+                    p.get("up_shift", 0.0), rt)
+
+
 register_part("feed_forward", "dense_mlp", _dense_mlp)
+register_part("feed_forward", "gated_mlp", _gated_mlp)
+register_part("feed_forward", "gated_moe", lambda p, store, rt: GatedMoE(p, store, rt))
+register_part("feed_forward", "none", lambda p, store, rt: NoFeedForward())

@@ -22,6 +22,13 @@ class TiedHead(Head):
         self.linear.forward(ctx, h, logits)
 
 
+class LinearHead(TiedHead):
+    """A head with a matrix of its own, [vocab, width], no bias."""
+
+
+register_part("head", "linear_head",
+              lambda p, store, rt: LinearHead(store.get(p["weights"], rt.dtype), p["vocab"],
+                                              p["width"], rt))
 register_part("head", "tied_head",
               lambda p, store, rt: TiedHead(store.get(p["weights"] + ".weight", rt.dtype),
                                             p["vocab"], p["width"], rt))

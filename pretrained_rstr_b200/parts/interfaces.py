@@ -26,6 +26,7 @@ class KVSpec:
     kv_heads: int
     head_dim: int
     window: Optional[int] = None      # None: all keys; w: only the last w
+    values: bool = True               # False: one row per token serves as key and value
 
 
 @dataclass(frozen=True)
@@ -43,7 +44,7 @@ class LayerCache:
     ``ctx.groups``), whether this run entry writes them, and its state tensors."""
     group: int = -1
     k: Optional[torch.Tensor] = None
-    v: Optional[torch.Tensor] = None
+    v: Optional[torch.Tensor] = None      # None for a mixer whose KVSpec says ``values=False``
     writes: bool = True
     state: Optional[dict] = None       # name -> tensor [slots, *shape]
 
@@ -68,7 +69,9 @@ class Mixer:
 
     def forward(self, ctx, h: torch.Tensor, x: torch.Tensor, cache: LayerCache) -> None:
         """x += mix(h) for the T tokens of the step, reading and (if ``cache.writes``)
-        extending the cache."""
+        extending the cache.  A part that sets ``can_overwrite = True`` also takes
+        ``accumulate=False``: x = mix(h) (arrangements that treat the branch before it joins
+        the stream ask for that)."""
         raise NotImplementedError
 
 
@@ -77,7 +80,8 @@ class FeedForward:
         return []
 
     def forward(self, ctx, h: torch.Tensor, x: torch.Tensor) -> None:
-        """x += feed_forward(h)."""
+        """x += feed_forward(h); with ``can_overwrite = True`` also ``accumulate=False``:
+        x = feed_forward(h)."""
         raise NotImplementedError
 
 
@@ -95,6 +99,14 @@ class PositionEncoding:
 
 
 class Embedding:
+    def state_specs(self) -> List[StateSpec]:
+        """Fixed-size per-request state the embedding keeps (the token before, say); the
+        tensors arrive through :meth:`bind_state`."""
+        return []
+
+    def bind_state(self, state: dict) -> None:
+        """``state``: name -> tensor [slots, *shape] of what ``state_specs`` declared."""
+
     def forward(self, ctx, position: PositionEncoding, x: torch.Tensor) -> None:
         """x[t] = table[token[t]] (+ position table row); x float32 [T, width]."""
         raise NotImplementedError

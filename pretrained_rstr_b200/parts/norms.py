@@ -31,4 +31,37 @@ def _layer_norm(params, store, runtime) -> LayerNorm:
     return LayerNorm(store.get(name + ".weight"), beta, params["eps"], params["size"])
 
 
+class RMSNorm(Norm):
+    """x / sqrt(mean(x^2) + eps), times one learned number (``gain``) and/or a learned weight
+    per coordinate; statistics in 32-bit.  ``joined`` is the same norm of a gated branch
+    joined to the stream: x <- norm(alpha x + sigmoid(gate) * y), with an optional copy of the
+    result in the activation type."""
+    graph_safe = True
+    kind = "rms_norm"
+
+    def __init__(self, gain, weight, eps: float, size: int):
+        if gain is not None and gain.numel() != 1:
+            raise ValueError("rms_norm: the gain is one number")
+        if weight is not None and weight.numel() != size:
+            raise ValueError(f"rms_norm: weight size differs from {size}")
+        self.gain = None if gain is None else gain.to(torch.float32).reshape(1).contiguous()
+        self.weight = None if weight is None else weight.to(torch.float32).contiguous()
+        self.eps, self.size = float(eps), size
+
+    def forward(self, ctx, x, out, rows=None) -> None:
+        ops.rms_norm(x, out=out, gain=self.gain, weight=self.weight, rows=rows, eps=self.eps,
+                     status=ctx.status)
+
+    def joined(self, ctx, x, y, alpha: float, gate=None, gate_bias=None, copy=None) -> None:
+        ops.rms_norm(x, out=copy, x_out=x, y=y, gate=gate, gate_bias=gate_bias, gain=self.gain,
+                     weight=self.weight, alpha=alpha, eps=self.eps, status=ctx.status)
+
+
+def _rms_norm(params, store, runtime) -> RMSNorm:
+    gain = store.get(params["gain"]) if params.get("gain") else None
+    weight = store.get(params["weight"]) if params.get("weight") else None
+    return RMSNorm(gain, weight, params["eps"], params["size"])
+
+
 register_part("norm", "layer_norm", _layer_norm)
+register_part("norm", "rms_norm", _rms_norm)

@@ -44,6 +44,7 @@ class WeightError(ValueError):
 class TensorExpectation:
     shape: Tuple[int, ...]
     kind: str = "float"          # "float" or "int"
+    optional: bool = False       # may be absent from the file (the part then does without it)
 
 
 def _stored_dtype(dtype: torch.dtype, kind: str) -> torch.dtype:
@@ -120,7 +121,7 @@ def load_weights(folder: str, expected: Dict[str, TensorExpectation], device,
             found[name] = stored_name
         elif not ignorable(name):
             unexpected.append(stored_name)
-    missing = sorted(n for n in expected if n not in found)
+    missing = sorted(n for n in expected if n not in found and not expected[n].optional)
     wrong: List[str] = []
     for name, stored_name in sorted(found.items()):
         exp = expected[name]
