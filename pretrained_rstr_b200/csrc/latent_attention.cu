@@ -80,10 +80,10 @@ latent_prepare_kernel(A* __restrict__ cq, long cq_ld, C* __restrict__ cache,
 }
 
 // grid (ceil(T / LA_GROUP), heads).  q: float32 [T, ld], head h at columns h*(dim+rot_dim);
-// uk: [heads*dim, rank]; qa: float32 [T, heads, rank + rot_dim].
-template <typename W>
+// uk: [heads*dim, rank]; qa: [T, heads, rank + rot_dim], float32 or (for the tensor-core kernel) bfloat16.
+template <typename W, typename O>
 __global__ void __launch_bounds__(LA_THREADS)
-latent_fold_kernel(float* __restrict__ qa, const float* __restrict__ q, long ld,
+latent_fold_kernel(O* __restrict__ qa, const float* __restrict__ q, long ld,
                    const W* __restrict__ uk, const int* __restrict__ positions,
                    const float* __restrict__ freq, int n_tokens, int heads, int dim, int rot_dim,
                    int rot_dims, int rank) {
@@ -107,7 +107,8 @@ latent_fold_kernel(float* __restrict__ qa, const float* __restrict__ q, long ld,
         }
 #pragma unroll
         for (int j = 0; j < LA_GROUP; ++j)
-            if (t0 + j < n_tokens) qa[((size_t)(t0 + j) * heads + h) * D + r] = acc[j];
+            if (t0 + j < n_tokens)
+                qa[((size_t)(t0 + j) * heads + h) * D + r] = prb_from_float<O>(acc[j]);
     }
     const int half = rot_dims / 2;
     for (int e = threadIdx.x; e < LA_GROUP * rot_dim; e += blockDim.x) {
@@ -126,7 +127,7 @@ latent_fold_kernel(float* __restrict__ qa, const float* __restrict__ q, long ld,
             sincosf(pos * freq[i - half], &sn, &cs);
             v = r[i] * cs + r[i - half] * sn;
         }
-        qa[((size_t)t * heads + h) * D + rank + i] = v;
+        qa[((size_t)t * heads + h) * D + rank + i] = prb_from_float<O>(v);
     }
 }
 
@@ -282,10 +283,10 @@ PRB_API int prb_latent_prepare(void* cq, long cq_ld, void* cache, const float* p
     return 0;
 }
 
-PRB_API int prb_latent_fold(float* qa, const float* q, long ld, const void* uk,
+PRB_API int prb_latent_fold(void* qa, const float* q, long ld, const void* uk,
                             const int* positions, const float* freq, int n_tokens, int heads,
                             int dim, int rot_dim, int rot_dims, int rank, int w_dtype,
-                            cudaStream_t stream) {
+                            int out_dtype, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (heads <= 0 || heads > 65535 || dim <= 0 || rank <= 0 || rot_dim < 0 || rot_dims > rot_dim ||
         rot_dims % 2 != 0)
@@ -293,13 +294,18 @@ PRB_API int prb_latent_fold(float* qa, const float* q, long ld, const void* uk,
     const size_t smem = (size_t)LA_GROUP * dim * sizeof(float);
     if (smem > 48 * 1024) return PRB_E_SIZE;
     dim3 grid((n_tokens + LA_GROUP - 1) / LA_GROUP, heads);
-    if (w_dtype == PRB_F32)
-        latent_fold_kernel<float><<<grid, LA_THREADS, smem, stream>>>(
-            qa, q, ld, (const float*)uk, positions, freq, n_tokens, heads, dim, rot_dim, rot_dims, rank);
-    else if (w_dtype == PRB_BF16)
-        latent_fold_kernel<__nv_bfloat16><<<grid, LA_THREADS, smem, stream>>>(
-            qa, q, ld, (const __nv_bfloat16*)uk, positions, freq, n_tokens, heads, dim, rot_dim,
+    if (w_dtype == PRB_F32 && out_dtype == PRB_F32)
+        latent_fold_kernel<float, float><<<grid, LA_THREADS, smem, stream>>>(
+            (float*)qa, q, ld, (const float*)uk, positions, freq, n_tokens, heads, dim, rot_dim,
             rot_dims, rank);
+    else if (w_dtype == PRB_BF16 && out_dtype == PRB_F32)
+        latent_fold_kernel<__nv_bfloat16, float><<<grid, LA_THREADS, smem, stream>>>(
+            (float*)qa, q, ld, (const __nv_bfloat16*)uk, positions, freq, n_tokens, heads, dim,
+            rot_dim, rot_dims, rank);
+    else if (w_dtype == PRB_BF16 && out_dtype == PRB_BF16)
+        latent_fold_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, LA_THREADS, smem, stream>>>(
+            (__nv_bfloat16*)qa, q, ld, (const __nv_bfloat16*)uk, positions, freq, n_tokens, heads,
+            dim, rot_dim, rot_dims, rank);
     else
         return PRB_E_DTYPE;
     PRB_LAUNCH_CHECK();

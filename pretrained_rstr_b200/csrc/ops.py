@@ -138,12 +138,18 @@ def _declare(h: ctypes.CDLL) -> None:
     h.prb_route.argtypes = [P, P, P, P, L, P, P, I, I, I, I, I, P]
     h.prb_latent_prepare.argtypes = [P, L, P, P, L, I, I, P, P, P, P, P, I, I, I, I, I, I, I, F,
                                      I, I, P, P]
-    h.prb_latent_fold.argtypes = [P, P, L, P, P, P, I, I, I, I, I, I, I, P]
+    h.prb_latent_fold.argtypes = [P, P, L, P, P, P, I, I, I, I, I, I, I, I, P]
+    h.prb_latent_attention_mma.argtypes = [P, P, P, P, P, P, P, P, P, I, P, P, P, I, I, I, I, I, I,
+                                           F, I, I, I, I, I, P, P]
+    h.prb_latent_mma_supports.argtypes = [I, I, I]
+    h.prb_latent_mma_single_kw.argtypes = [I]
+    h.prb_latent_mma_rows.argtypes = []
     h.prb_latent_attention.argtypes = [P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, I, P, P]
     h.prb_latent_unfold.argtypes = [P, L, P, P, P, L, I, I, I, I, I, I, P]
     for name in ("prb_embed_pair", "prb_rms_norm", "prb_gated_pair", "prb_route",
                  "prb_latent_prepare", "prb_latent_fold", "prb_latent_attention",
-                 "prb_latent_unfold"):
+                 "prb_latent_unfold", "prb_latent_attention_mma", "prb_latent_mma_supports",
+                 "prb_latent_mma_single_kw", "prb_latent_mma_rows"):
         getattr(h, name).restype = c_int
     for name in ("prb_resolve_tokens", "prb_fetch_step", "prb_publish_result", "prb_embed", "prb_layernorm", "prb_bias_act", "prb_kv_append", "prb_copy_pages",
                  "prb_gemm_f32", "prb_gemm_bf16", "prb_gemm_bf16_scatter", "prb_gemm_midm",
@@ -958,17 +964,17 @@ def latent_fold(qa, q, uk, positions, freq, heads: int, dim: int, rot_dim: int, 
                 rank: int) -> None:
     """qa[t, h, :rank] = Uk_h^T q[t, h, :dim]; qa[t, h, rank:] = q[t, h, dim:] rotated by the
     token's position.  q float32 [T, heads * (dim + rot_dim)]; uk [heads * dim, rank];
-    qa float32 [T, heads, rank + rot_dim]."""
+    qa [T, heads, rank + rot_dim], float32 or bfloat16."""
     what = "latent_fold"
     if q.dtype != torch.float32 or q.stride(1) != 1 or q.shape[1] != heads * (dim + rot_dim):
         raise KernelArgumentError(f"{what}: q must be float32 [T, heads * (dim + rot_dim)]")
-    _need(qa, torch.float32, "qa", what)
+    _need(qa, None, "qa", what)
     _need(uk, None, "uk", what)
     if tuple(uk.shape) != (heads * dim, rank) or tuple(qa.shape) != (q.shape[0], heads, rank + rot_dim):
         raise KernelArgumentError(f"{what}: shapes do not fit")
     _check(lib().prb_latent_fold(_p(qa), _p(q), q.stride(0), _p(uk), _p(positions), _p(freq),
                                  q.shape[0], heads, dim, rot_dim, rot_dims, rank,
-                                 dtype_code(uk.dtype), _stream()), what)
+                                 dtype_code(uk.dtype), dtype_code(qa.dtype), _stream()), what)
 
 
 def latent_attention(out, qa, cache, block_table, seq_of_token, positions, sinks, scale: float,
@@ -1003,7 +1009,7 @@ def latent_unfold(out, lat, uvt, gate, heads: int, rank: int, vdim: int) -> None
     _need(lat, torch.float32, "lat", what)
     _need(uvt, None, "uvt", what)
     if tuple(uvt.shape) != (heads, rank, vdim) or tuple(lat.shape[1:]) != (heads, rank) or \
-            out.stride(1) != 1 or out.shape[1] != heads * vdim or out.shape[0] < lat.shape[0]:
+            out.stride(1) != 1 or out.shape[1] < heads * vdim or out.shape[0] < lat.shape[0]:
         raise KernelArgumentError(f"{what}: shapes do not fit")
     gate_ld = 0
     if gate is not None:
@@ -1013,3 +1019,61 @@ def latent_unfold(out, lat, uvt, gate, heads: int, rank: int, vdim: int) -> None
     _check(lib().prb_latent_unfold(_p(out), out.stride(0), _p(lat), _p(uvt), _p(gate), gate_ld,
                                    lat.shape[0], heads, rank, vdim, dtype_code(uvt.dtype),
                                    dtype_code(out.dtype), _stream()), what)
+
+
+def latent_mma_supports(heads: int, rank: int, rot_dim: int) -> bool:
+    """Whether ``latent_attention_mma`` takes these sizes (up to 64 heads, rank a multiple of 16
+    up to 256, rotated part a multiple of 16)."""
+    return bool(lib().prb_latent_mma_supports(int(heads), int(rank), int(rot_dim)))
+
+
+def latent_mma_single_kw(heads: int) -> int:
+    """Into how many parts the warps of a CTA split a key block for single tokens."""
+    return int(lib().prb_latent_mma_single_kw(int(heads)))
+
+
+def latent_mma_rows() -> int:
+    """Rows ((token, head) pairs) of a work item of ``latent_attention_mma``."""
+    return int(lib().prb_latent_mma_rows())
+
+
+def latent_attention_mma(out, qa, cache, block_table, seq_of_token, positions, item_row0,
+                         item_tokens, item_count, n_items: int, sinks, ws_o, ws_ml, scale: float,
+                         window, rank: int, split_keys: int, splits: int, kw: int, ws_rows: int,
+                         status) -> None:
+    """The same as ``latent_attention`` on tensor cores for bfloat16 queries and cache.  Work
+    items: item i is ``item_tokens[i]`` (1 if None) consecutive tokens of one request from
+    token row ``item_row0[i]`` on, all heads (heads * tokens <= ``ws_rows`` <= 64); ``n_items``
+    are launched, ``item_count`` (device int32, or None) bounds them.  Keys go in ``splits``
+    ranges of ``split_keys`` positions (a multiple of 64) to a CTA each, whose warps split every
+    block of 64 keys ``kw`` ways (1: prompt portions; 4 or 2: single tokens of up to 16 or 32
+    heads).  ``ws_o`` float32 [n_items * ws_rows * splits * kw * rank] and ``ws_ml`` (the same
+    without rank, times 2) hold the partial results a second kernel joins into ``out``."""
+    what = "latent_attention_mma"
+    _need(out, torch.float32, "out", what)
+    _need(qa, torch.bfloat16, "qa", what)
+    _need(cache, torch.bfloat16, "cache", what)
+    num_pages, kv_heads, page_size, row = cache.shape
+    n, heads, d = qa.shape
+    if kv_heads != 1 or row != d or tuple(out.shape) != (n, heads, rank) or rank > d:
+        raise KernelArgumentError(f"{what}: shapes do not fit")
+    _need(item_row0, torch.int32, "item_row0", what)
+    if item_tokens is not None:
+        _need(item_tokens, torch.int32, "item_tokens", what)
+    if item_row0.numel() < n_items or (item_tokens is not None and item_tokens.numel() < n_items):
+        raise KernelArgumentError(f"{what}: the work list is shorter than {n_items} items")
+    parts = int(splits) * int(kw)
+    _need(ws_o, torch.float32, "ws_o", what)
+    _need(ws_ml, torch.float32, "ws_ml", what)
+    if ws_o.numel() < n_items * ws_rows * parts * rank or ws_ml.numel() < n_items * ws_rows * parts * 2:
+        raise KernelArgumentError(f"{what}: the workspace is too small")
+    if sinks is not None:
+        _need(sinks, torch.float32, "sinks", what)
+    code = lib().prb_latent_attention_mma(
+        _p(out), _p(qa), _p(cache), _p(block_table), _p(seq_of_token), _p(positions), _p(item_row0),
+        _p(item_tokens), _p(item_count), int(n_items), _p(sinks), _p(ws_o), _p(ws_ml), heads, rank,
+        d - rank, page_size, block_table.shape[1], num_pages, float(scale), int(window or 0),
+        int(split_keys), int(splits), int(kw), int(ws_rows), _p(status), _stream())
+    _check(code, what)
+    if code == 0 and n_items > 0:
+        add_launches(1)                      # the kernel that joins the partial results

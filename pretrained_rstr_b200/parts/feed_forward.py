@@ -7,7 +7,7 @@ import torch
 
 from ..csrc import ops
 from .interfaces import FeedForward
-from .linear import Linear
+from .linear import Linear, padded_linear
 from .registry import register_part
 
 
@@ -70,7 +70,7 @@ class GatedMLP(FeedForward):
         self.input = FusedInput(width, runtime, "gated_in")
         self.input.add("gate", gate)
         self.input.add("up", up)
-        self.down = Linear(down, None, runtime)
+        self.down = padded_linear(down, runtime)
         self.width, self.inner = width, inner
         self.limit, self.act_alpha, self.up_shift = float(limit), float(act_alpha), float(up_shift)
         self.runtime = runtime
@@ -85,7 +85,7 @@ class GatedMLP(FeedForward):
         t = x.shape[0]
         proj = self._proj = self.input.run(ctx, h)
         cols = self.input.cols
-        a = ctx.scratch("gated_act", (ctx.token_capacity, self.inner), self.runtime.dtype)[:t]
+        a = ctx.scratch_zero("gated_act", (ctx.token_capacity, self.down.n_in), self.runtime.dtype)[:t]
         ops.gated_pair(a, proj, cols["gate"][0], cols["up"][0], self.inner, limit=self.limit,
                        act_alpha=self.act_alpha, up_shift=self.up_shift)
         self.down.forward(ctx, a, x, resid=x if accumulate else None)
@@ -130,7 +130,7 @@ class GatedMoE(FeedForward):
             downs.append(need("shared.down", (width, self.shared_inner)))
         self.input.add("router", need("router", (n, width)))
         self.router_bias = need("router.b", (n,)).to(torch.float32).contiguous()
-        self.down = Linear(torch.cat(downs, dim=1), None, runtime)
+        self.down = padded_linear(torch.cat(downs, dim=1), runtime)
 
     def fuse_input_rows(self, name: str, weight) -> str:
         return self.input.add(name, weight)
@@ -149,7 +149,7 @@ class GatedMoE(FeedForward):
         ops.route(scale, chosen, chosen_w, self.input.view(proj, "router"), None, self.router_bias,
                   self.top)
         n_act = self.experts * self.inner
-        a = ctx.scratch("moe_act", (cap, n_act + self.shared_inner), self.runtime.dtype)[:t]
+        a = ctx.scratch_zero("moe_act", (cap, self.down.n_in), self.runtime.dtype)[:t]
         ops.gated_pair(a, proj, cols["gate"][0], cols["up"][0], n_act, limit=self.limit,
                        act_alpha=self.act_alpha, up_shift=self.up_shift, scale=scale,
                        group=self.inner)

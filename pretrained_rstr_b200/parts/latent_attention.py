@@ -20,13 +20,15 @@ asks to ride along (:meth:`fuse_input_rows`); its float32 result feeds the norms
 """
 from __future__ import annotations
 
-from typing import Dict, List, Optional, Tuple
+from typing import Dict, List, Optional, Sequence, Tuple
 
+import numpy as np
 import torch
 
 from ..csrc import ops
+from ..engine.batch import WorkPlanner
 from .interfaces import KVSpec, LayerCache, Mixer
-from .linear import Linear
+from .linear import Linear, padded_linear
 from .registry import register_part
 
 
@@ -80,6 +82,80 @@ class FusedInput:
         return out[:, at:at + n]
 
 
+class LatentWork(WorkPlanner):
+    """How the tensor-core kernel cuts a step.  A request that brings one token is a
+    "single": an item of its own whose CTAs split the keys.  A portion of a prompt goes in
+    "tiles" of consecutive tokens, as many as fit a CTA's 64 (token, head) rows: 64 // heads,
+    so mixers with other head counts have lists of their own (``tile_row0_<tokens>``)."""
+
+    key = "latent_attention"
+    ROWS = 64
+
+    def __init__(self):
+        self.tile_tokens = set()           # tokens per tile of the mixers that use the lists
+
+    def note_mixer(self, heads: int) -> int:
+        tq = max(1, self.ROWS // int(heads))
+        self.tile_tokens.add(tq)
+        return tq
+
+    def absorb(self, other: "LatentWork") -> None:
+        self.tile_tokens |= other.tile_tokens
+
+    @property
+    def counters(self):
+        return ("singles",) + tuple(f"tiles_{tq}" for tq in sorted(self.tile_tokens))
+
+    def arrays(self, t_cap: int, b_cap: int):
+        out = {"single_row0": (min(t_cap, b_cap), 0)}
+        for tq in sorted(self.tile_tokens):
+            cap = t_cap // tq + b_cap
+            out[f"tile_row0_{tq}"] = (cap, 0)
+            out[f"tile_tokens_{tq}"] = (cap, 0)
+        return out
+
+    def fill(self, arrays: Dict[str, np.ndarray], lengths: Sequence[int]) -> Dict[str, int]:
+        counts = {name: 0 for name in self.counters}
+        used = []
+        if max(lengths) == 1:                   # a decode step
+            n = len(lengths)
+            arrays["single_row0"][:n] = np.arange(n, dtype=np.int32)
+            counts["singles"] = n
+            return {**counts, "_used": ["single_row0"]}
+        t = 0
+        sing = arrays["single_row0"]
+        for n in lengths:
+            if n == 1:
+                sing[counts["singles"]] = t
+                counts["singles"] += 1
+            else:
+                for tq in self.tile_tokens:
+                    row0, toks = arrays[f"tile_row0_{tq}"], arrays[f"tile_tokens_{tq}"]
+                    k = counts[f"tiles_{tq}"]
+                    for r0 in range(0, n, tq):
+                        row0[k] = t + r0
+                        toks[k] = min(tq, n - r0)
+                        k += 1
+                    counts[f"tiles_{tq}"] = k
+            t += n
+        if counts["singles"]:
+            used.append("single_row0")
+        for tq in self.tile_tokens:
+            if counts[f"tiles_{tq}"]:
+                used += [f"tile_row0_{tq}", f"tile_tokens_{tq}"]
+        return {**counts, "_used": used}
+
+
+def key_splits(items: int, max_context: int, most: int, sm_count: int):
+    """(keys per range, ranges) for a launch of ``items`` work items over contexts of up to
+    ``max_context`` keys: about two CTAs per SM, ranges of whole 64-key blocks, at least four
+    blocks long unless the context is shorter."""
+    blocks = max(1, -(-max_context // 64))
+    wanted = max(1, min(most, -(-2 * sm_count // max(1, items)), max(1, blocks // 4)))
+    split_keys = -(-blocks // wanted) * 64
+    return split_keys, -(-blocks * 64 // split_keys)
+
+
 class LatentAttention(Mixer):
     graph_safe = True
     can_overwrite = True
@@ -109,7 +185,7 @@ class LatentAttention(Mixer):
             self.input.add("gate", need("gate", (self.heads, self.width)))
         self.q_norm = need("q_norm", (self.q_rank,)).to(torch.float32).contiguous()
         self.kv_norm = need("kv_norm", (self.rank,)).to(torch.float32).contiguous()
-        self.q_up = Linear(need("q_up", (self.heads * hd, self.q_rank)), None, runtime)
+        self.q_up = padded_linear(need("q_up", (self.heads * hd, self.q_rank)), runtime)
         self.uk = need("k_up", (self.heads * self.dim, self.rank)).to(dtype).contiguous()
         # the value expansion with the latent axis outermost: a thread per value coordinate
         # then reads neighbouring numbers
@@ -117,11 +193,21 @@ class LatentAttention(Mixer):
             .reshape(self.heads, self.vdim, self.rank).transpose(1, 2).contiguous()
         self.sinks = need("sink", (self.heads,)).to(torch.float32).contiguous() \
             if p.get("sink", False) else None
-        self.out = Linear(need("out", (self.width, self.heads * self.vdim)), None, runtime)
+        self.out = padded_linear(need("out", (self.width, self.heads * self.vdim)), runtime)
         half = self.rot_dims // 2
         base = float(p.get("rot_base", 10000.0))
         self.freq = torch.tensor([base ** (-2.0 * i / self.rot_dims) for i in range(half)] or [0.0],
                                  dtype=torch.float64).to(torch.float32).to(dev)
+        # bfloat16 serving: the tensor-core kernel where it takes the sizes, else (and in
+        # float32) the 32-bit-arithmetic kernel
+        self.tensor_cores = dtype == torch.bfloat16 and torch.cuda.is_available() and \
+            ops.latent_mma_supports(self.heads, self.rank, self.rot_dim)
+        self.work_plan = LatentWork()
+        self.tile_tokens = self.work_plan.note_mixer(self.heads)
+        self.sm_count = ops.sm_count() if torch.cuda.is_available() else 148
+
+    def work_planners(self):
+        return [self.work_plan] if self.tensor_cores else []
 
     # ------------------------------------------------------------------ structure
     def kv_spec(self) -> KVSpec:
@@ -142,7 +228,7 @@ class LatentAttention(Mixer):
         group = ctx.groups[cache.group]
         proj = self._proj = self.input.run(ctx, h)
         cols = self.input.cols
-        cq = ctx.scratch("latent_cq", (cap, self.q_rank), dtype)[:t]
+        cq = ctx.scratch_zero("latent_cq", (cap, self.q_up.n_in), dtype)[:t]
         ops.latent_prepare(cq, cache.k, proj, cols["q"][0], cols["kv"][0], self.q_norm,
                            self.kv_norm, group.slots if cache.writes else None, ctx.positions,
                            self.freq, self.q_rank, self.rank, self.rot_dim, self.rot_dims,
@@ -150,15 +236,49 @@ class LatentAttention(Mixer):
         q = ctx.scratch("latent_q", (cap, self.q_up.n_out), torch.float32)[:t]
         self.q_up.forward(ctx, cq, q)
         qa = ctx.scratch("latent_qa", (cap, self.heads, self.rank + self.rot_dim),
-                         torch.float32)[:t]
+                         dtype if self.tensor_cores else torch.float32)[:t]
         ops.latent_fold(qa, q, self.uk, ctx.positions, self.freq, self.heads, self.dim,
                         self.rot_dim, self.rot_dims, self.rank)
         lat = ctx.scratch("latent_sum", (cap, self.heads, self.rank), torch.float32)[:t]
-        attend_latent(ctx, lat, qa, cache, group, self.sinks, self.scale, self.window, self.rank)
-        o = ctx.scratch("latent_o", (cap, self.heads * self.vdim), dtype)[:t]
+        if self.tensor_cores:
+            self._attend_tensor_cores(ctx, lat, qa, cache, group)
+        else:
+            attend_latent(ctx, lat, qa, cache, group, self.sinks, self.scale, self.window, self.rank)
+        o = ctx.scratch_zero("latent_o", (cap, self.out.n_in), dtype)[:t]
         gate = self.input.view(proj, "gate") if self.head_gate else None
         ops.latent_unfold(o, lat, self.uvt, gate, self.heads, self.rank, self.vdim)
         self.out.forward(ctx, o, x, resid=x if accumulate else None)
+
+
+    #: most key ranges of a launch: single tokens, prompt tiles
+    MAX_SPLITS = (16, 8)
+
+    def _attend_tensor_cores(self, ctx, lat, qa, cache: LayerCache, group) -> None:
+        """Single tokens and prompt tiles as two launches (each only if the step has such
+        work; a step that is replayed from a graph launches a list's capacity and lets the
+        device-side count bound it)."""
+        work = ctx.work[LatentWork.key]
+        tq = self.tile_tokens
+        lists = (("singles", "single_row0", None, ops.latent_mma_single_kw(self.heads), self.heads,
+                  self.MAX_SPLITS[0]),
+                 (f"tiles_{tq}", f"tile_row0_{tq}", f"tile_tokens_{tq}", 1, LatentWork.ROWS,
+                  self.MAX_SPLITS[1]))
+        for counter, rows_name, tokens_name, kw, ws_rows, most in lists:
+            count = work.host_counts[counter]
+            if count == 0:
+                continue
+            cap = work.caps[rows_name]
+            n = cap if count is None else count
+            most = max(1, min(most, 2 * self.sm_count // cap))     # (bounds the workspace too)
+            split_keys, splits = key_splits(n, ctx.max_context, most, self.sm_count)
+            slots = cap * ws_rows * most * kw
+            ws_o = ctx.scratch("latent_part_o", (slots * self.rank,), torch.float32)
+            ws_ml = ctx.scratch("latent_part_ml", (slots * 2,), torch.float32)
+            ops.latent_attention_mma(
+                lat, qa, cache.k, group.block_table, ctx.seq_of_token, ctx.positions,
+                work.arrays[rows_name], work.arrays[tokens_name] if tokens_name else None,
+                work.counts[counter], n, self.sinks, ws_o, ws_ml, self.scale, self.window,
+                self.rank, split_keys, splits, kw, ws_rows, ctx.status)
 
 
 def attend_latent(ctx, lat, qa, cache: LayerCache, group, sinks, scale: float,

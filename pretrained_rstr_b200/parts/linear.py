@@ -93,6 +93,19 @@ class Linear:
         return kv_scatter is not None
 
 
+def padded_linear(weight: torch.Tensor, runtime) -> Linear:
+    """A Linear over ``weight`` [out, in] whose input width is rounded up to a multiple of 8
+    with zero columns (what the tensor-core kernels read in 16-byte pieces).  The caller keeps
+    its input in a buffer of ``n_in`` columns from ``ctx.scratch_zero`` and writes the real
+    columns only: the rest stay zero."""
+    k = weight.shape[1]
+    k_pad = -(-k // 8) * 8
+    if k_pad != k:
+        weight = torch.cat([weight, torch.zeros((weight.shape[0], k_pad - k), dtype=weight.dtype,
+                                                device=weight.device)], dim=1)
+    return Linear(weight, None, runtime)
+
+
 class LazyNorm:
     """A norm of ``x`` (of its rows ``rows``, if given: an int32 tensor of row indices) that
     runs when its result is first needed.  A consumer that can compute the norm itself

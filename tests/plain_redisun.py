@@ -145,7 +145,20 @@ def residual_gate(h, tensors, name: str) -> torch.Tensor:
     return torch.sigmoid(h @ tensors[name].to(h.dtype).T + tensors[name + ".b"].to(h.dtype))
 
 
-def layer(x: torch.Tensor, tensors, i: int, spec: dict, cfg: dict) -> torch.Tensor:
+def router_gap(h: torch.Tensor, tensors, prefix: str, mlp: dict) -> torch.Tensor:
+    """Per token, how far the last chosen expert's logit lies above the first one left out
+    (infinite when all are chosen): a choice with a small gap may fall either way once the
+    input is rounded."""
+    top = int(mlp["router"]["top"])
+    _, _, z = route(h, tensors, prefix, top)
+    if top >= z.shape[1]:
+        return torch.full((h.shape[0],), float("inf"), dtype=h.dtype)
+    ordered = torch.sort(z, dim=-1, descending=True).values
+    return ordered[:, top - 1] - ordered[:, top]
+
+
+def layer(x: torch.Tensor, tensors, i: int, spec: dict, cfg: dict,
+          gaps: Optional[list] = None) -> torch.Tensor:
     """Norm after the sum, the branch gated: x <- norm(alpha x + gate(x) * branch(x))."""
     p = f"l{i}."
     eps, alpha = float(cfg["norm"]["eps"]), float(cfg["postln_alpha"])
@@ -154,18 +167,67 @@ def layer(x: torch.Tensor, tensors, i: int, spec: dict, cfg: dict) -> torch.Tens
     y = latent_attention(x, tensors, p, spec["mixer"], eps) * residual_gate(x, tensors, p + "rg1")
     x = scalar_norm(alpha * x + y, tensors[p + "norm1"].to(x.dtype), eps)
     if spec.get("mlp"):
+        if gaps is not None and spec["mlp"]["kind"] == "moe":
+            gaps.append(router_gap(x, tensors, p + "mlp.", spec["mlp"]))
         y = feed_forward(x, tensors, p, spec["mlp"]) * residual_gate(x, tensors, p + "rg2")
         x = scalar_norm(alpha * x + y, tensors[p + "norm2"].to(x.dtype), eps)
     return x
 
 
 def forward(tokens: List[int], tensors, cfg: dict, dtype=torch.float64,
-            streams: Optional[list] = None) -> torch.Tensor:
-    """Logits [T, vocab] of one whole sequence; ``streams`` collects x after every layer."""
+            streams: Optional[list] = None, gaps: Optional[list] = None) -> torch.Tensor:
+    """Logits [T, vocab] of one whole sequence; ``streams`` collects x after every layer,
+    ``gaps`` every routed layer's :func:`router_gap`."""
     x = embed(tokens, tensors, cfg, dtype)
     for i, spec in enumerate(cfg["layers"]):
-        x = layer(x, tensors, i, spec, cfg)
+        x = layer(x, tensors, i, spec, cfg, gaps)
         if streams is not None:
             streams.append(x.clone())
     x = scalar_norm(x, tensors["final.norm"].to(dtype), float(cfg["norm"]["eps"]))
     return x @ tensors["head"].to(dtype).T
+
+
+# ------------------------------------------------------------------ reading a model folder
+def read_folder(folder: str):
+    """(config dict, tensors by name as float32 / int32 torch tensors) of a model folder, read
+    with nothing but the file format: 8 bytes of header length, a JSON header, the data."""
+    import json
+    import os
+    import struct
+
+    import numpy as np
+    with open(os.path.join(folder, "config.json"), "r", encoding="utf-8") as fh:
+        cfg = json.load(fh)
+    with open(os.path.join(folder, "model.safetensors"), "rb") as fh:
+        (n,) = struct.unpack("<Q", fh.read(8))
+        header = json.loads(fh.read(n))
+        data = fh.read()
+    tensors = {}
+    for name, entry in header.items():
+        if name == "__metadata__":
+            continue
+        lo, hi = entry["data_offsets"]
+        raw = data[lo:hi]
+        if entry["dtype"] == "BF16":
+            bits = np.frombuffer(raw, dtype="<u2").astype(np.uint32) << 16
+            t = torch.from_numpy(bits.view(np.float32).copy())
+        elif entry["dtype"] == "F32":
+            t = torch.from_numpy(np.frombuffer(raw, dtype="<f4").copy())
+        elif entry["dtype"] == "I32":
+            t = torch.from_numpy(np.frombuffer(raw, dtype="<i4").copy())
+        else:
+            raise ValueError(f"{name}: dtype {entry['dtype']}")
+        tensors[name] = t.reshape(entry["shape"])
+    return cfg, tensors
+
+
+def greedy(tokens: List[int], n: int, tensors, cfg: dict) -> List[int]:
+    """n tokens chosen by largest logit (lowest id among equals), the whole sequence run anew
+    for every token."""
+    ids, out = list(tokens), []
+    for _ in range(n):
+        row = forward(ids, tensors, cfg)[-1]
+        best = int((row == row.max()).nonzero()[0])
+        out.append(best)
+        ids.append(best)
+    return out
