@@ -4,6 +4,7 @@ for GPT-2 small with random weights, each with its fraction of the roofline.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl reference]
     python bench.py --workload mixed [--size medium] [--pool-fraction 0.4]
+    python bench.py --compare small,redisun-small,redisun-small-moe [--kernels]
 
 Prints ONE JSON line.  A "step" is one decode step of the whole batch.  ``value`` is
 decoded tokens per second from device time (CUDA events around each step's kernels);
@@ -19,6 +20,11 @@ plus cache are larger than the 126 MB L2, so no flush is needed between timed st
 ``--workload mixed`` runs many requests of unequal length through the scheduler (prompts
 uniform in [16, 1024), portions of 512 beside decoding requests, 30 % sharing a 256-token
 prefix) and reports times to first token, step times by kind and the cache's counters.
+
+``--compare A,B,...`` measures named sizes of any registered design side by side (prefill of
+2 x 1,024 tokens, decoding at batch 1, 8 and 64 near 1,000 tokens of context, each with its
+fraction of the roofline counted from the model's own tensors and cache rows); ``--kernels``
+adds the device time of every kernel of a decode step and a prompt step.
 
 The code that measures lives in ``pretrained_rstr_b200/measure/``; the ``--profile-*``
 options run its small single-kernel workloads (for profiler captures).
@@ -108,6 +114,28 @@ def run_mixed(args) -> int:
     return 0
 
 
+def run_compare(args) -> int:
+    """Named sizes side by side: one JSON line."""
+    from pretrained_rstr_b200.measure.designs import kernel_table, measure_size
+    names = [n.strip() for n in args.compare.split(",") if n.strip()]
+    designs, kernels = {}, {}
+    with ClockSampler() as clocks:
+        for name in names:
+            designs[name] = measure_size(name, steps=args.steps, warmup=args.warmup,
+                                         layers=args.layers)
+            if args.kernels:
+                kernels[name] = kernel_table(name, layers=args.layers)
+    pk = peaks()
+    record = {"workload": "compare", "dtype": "bf16", "data": "synthetic", "n_gpus": 1,
+              "steps": args.steps, "warmup": args.warmup, "peaks": {k: pk[k] for k in
+                                                                    ("hbm_gbs", "bf16_tflops", "source")},
+              "designs": designs, "clocks": clocks.summary()}
+    if kernels:
+        record["kernels"] = kernels
+    print(json.dumps(record))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--profile-prefill", action="store_true")
@@ -145,6 +173,10 @@ def main() -> int:
     ap.add_argument("--temperature", type=float, default=None,
                     help="decode with temperature sampling (top-k 40) instead of greedy")
     ap.add_argument("--quick", action="store_true", help="only the headline point and the prefill")
+    ap.add_argument("--compare", default=None, metavar="SIZE,SIZE,...",
+                    help="named sizes of any design side by side (e.g. small,redisun-small)")
+    ap.add_argument("--kernels", action="store_true",
+                    help="with --compare: device time by kernel of a decode and a prompt step")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
@@ -170,6 +202,8 @@ def main() -> int:
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    if args.compare:
+        return run_compare(args)
     if args.workload == "mixed":
         return run_mixed(args)
 
