@@ -23,6 +23,10 @@ namespace {
 constexpr int LA_THREADS = 128;
 constexpr int LA_GROUP = 8;          // tokens that share a CTA's pass over a head's matrix
 constexpr int LA_MAX_ACC = 8;        // rank <= LA_THREADS * LA_MAX_ACC
+constexpr int LA_OUT = 32;           // outputs a CTA of the fold / unfold makes (one per lane)
+constexpr int LA_SLICES = LA_THREADS / 32;   // parts of the reduction (one per warp)
+constexpr int LU_THREADS = 256;      // the unfold's reduction is the longer one: eight warps
+constexpr int LU_SLICES = LU_THREADS / 32;
 
 __device__ __forceinline__ float la_sigmoid(float z) { return 1.0f / (1.0f + expf(-z)); }
 
@@ -79,8 +83,13 @@ latent_prepare_kernel(A* __restrict__ cq, long cq_ld, C* __restrict__ cache,
     }
 }
 
-// grid (ceil(T / LA_GROUP), heads).  q: float32 [T, ld], head h at columns h*(dim+rot_dim);
-// uk: [heads*dim, rank]; qa: [T, heads, rank + rot_dim], float32 or (for the tensor-core kernel) bfloat16.
+// grid (ceil(T / LA_GROUP), heads, ceil(rank / LA_OUT) + 1).  q: float32 [T, ld], head h at
+// columns h*(dim+rot_dim); uk: [heads*dim, rank]; qa: [T, heads, rank + rot_dim], float32 or
+// (for the tensor-core kernel) bfloat16.  A CTA makes LA_OUT coordinates of the folded query
+// for LA_GROUP tokens of one head: lane = coordinate, warp = a quarter of the head's `dim`
+// (every fourth d), the quarters summed in warp order through shared memory; the loads of a
+// thread's weights do not depend on one another, so they are all in flight at once.  The last
+// z-block rotates the rest of the head's query.
 template <typename W, typename O>
 __global__ void __launch_bounds__(LA_THREADS)
 latent_fold_kernel(O* __restrict__ qa, const float* __restrict__ q, long ld,
@@ -88,46 +97,61 @@ latent_fold_kernel(O* __restrict__ qa, const float* __restrict__ q, long ld,
                    const float* __restrict__ freq, int n_tokens, int heads, int dim, int rot_dim,
                    int rot_dims, int rank) {
     extern __shared__ float qs[];                        // [LA_GROUP][dim]
+    __shared__ float part[LA_SLICES][LA_GROUP][LA_OUT];
     const int t0 = blockIdx.x * LA_GROUP, h = blockIdx.y;
     const int hd = dim + rot_dim, D = rank + rot_dim;
+    if ((int)blockIdx.z * LA_OUT >= rank) {              // the rotated part
+        const int half = rot_dims / 2;
+        for (int e = threadIdx.x; e < LA_GROUP * rot_dim; e += blockDim.x) {
+            const int j = e / rot_dim, i = e - j * rot_dim;
+            const int t = t0 + j;
+            if (t >= n_tokens) continue;
+            const float* r = q + (size_t)t * ld + h * hd + dim;
+            const float pos = (float)positions[t];
+            float v = r[i];
+            if (i < half) {
+                float sn, cs;
+                sincosf(pos * freq[i], &sn, &cs);
+                v = r[i] * cs - r[i + half] * sn;
+            } else if (i < rot_dims) {
+                float sn, cs;
+                sincosf(pos * freq[i - half], &sn, &cs);
+                v = r[i] * cs + r[i - half] * sn;
+            }
+            qa[((size_t)t * heads + h) * D + rank + i] = prb_from_float<O>(v);
+        }
+        return;
+    }
     for (int e = threadIdx.x; e < LA_GROUP * dim; e += blockDim.x) {
         const int j = e / dim, d = e - j * dim;
         qs[e] = (t0 + j < n_tokens) ? q[(size_t)(t0 + j) * ld + h * hd + d] : 0.0f;
     }
     __syncthreads();
-    for (int r = threadIdx.x; r < rank; r += blockDim.x) {
-        float acc[LA_GROUP];
+    const int lane = threadIdx.x & 31, slice = threadIdx.x >> 5;
+    const int r = blockIdx.z * LA_OUT + lane;
+    float acc[LA_GROUP];
 #pragma unroll
-        for (int j = 0; j < LA_GROUP; ++j) acc[j] = 0.0f;
+    for (int j = 0; j < LA_GROUP; ++j) acc[j] = 0.0f;
+    if (r < rank) {
         const W* w = uk + (size_t)h * dim * rank + r;
-        for (int d = 0; d < dim; ++d) {
+#pragma unroll 8
+        for (int d = slice; d < dim; d += LA_SLICES) {
             const float wv = prb_to_float<W>(w[(size_t)d * rank]);
 #pragma unroll
             for (int j = 0; j < LA_GROUP; ++j) acc[j] = fmaf(qs[j * dim + d], wv, acc[j]);
         }
-#pragma unroll
-        for (int j = 0; j < LA_GROUP; ++j)
-            if (t0 + j < n_tokens)
-                qa[((size_t)(t0 + j) * heads + h) * D + r] = prb_from_float<O>(acc[j]);
     }
-    const int half = rot_dims / 2;
-    for (int e = threadIdx.x; e < LA_GROUP * rot_dim; e += blockDim.x) {
-        const int j = e / rot_dim, i = e - j * rot_dim;
-        const int t = t0 + j;
-        if (t >= n_tokens) continue;
-        const float* r = q + (size_t)t * ld + h * hd + dim;
-        const float pos = (float)positions[t];
-        float v = r[i];
-        if (i < half) {
-            float sn, cs;
-            sincosf(pos * freq[i], &sn, &cs);
-            v = r[i] * cs - r[i + half] * sn;
-        } else if (i < rot_dims) {
-            float sn, cs;
-            sincosf(pos * freq[i - half], &sn, &cs);
-            v = r[i] * cs + r[i - half] * sn;
-        }
-        qa[((size_t)t * heads + h) * D + rank + i] = prb_from_float<O>(v);
+#pragma unroll
+    for (int j = 0; j < LA_GROUP; ++j) part[slice][j][lane] = acc[j];
+    __syncthreads();
+    for (int e = threadIdx.x; e < LA_GROUP * LA_OUT; e += blockDim.x) {
+        const int j = e / LA_OUT, l = e - j * LA_OUT;
+        const int rr = blockIdx.z * LA_OUT + l;
+        if (t0 + j >= n_tokens || rr >= rank) continue;
+        float v = part[0][j][l];
+#pragma unroll
+        for (int sl = 1; sl < LA_SLICES; ++sl) v += part[sl][j][l];
+        qa[((size_t)(t0 + j) * heads + h) * D + rr] = prb_from_float<O>(v);
     }
 }
 
@@ -223,38 +247,50 @@ latent_attention_kernel(float* __restrict__ out, const float* __restrict__ qa,
     }
 }
 
-// grid (ceil(T / LA_GROUP), heads).  lat: float32 [T, heads, rank]; uvt: [heads, rank, vdim]
-// (the value expansion with the latent axis outermost); out: [T, heads*vdim] in O;
-// gate: float32, head h of token t at gate[t*gate_ld + h], or null.
+// grid (ceil(T / LA_GROUP), heads, ceil(vdim / LA_OUT)).  lat: float32 [T, heads, rank]; uvt:
+// [heads, rank, vdim] (the value expansion with the latent axis outermost); out: [T,
+// heads*vdim] in O; gate: float32, head h of token t at gate[t*gate_ld + h], or null.  Like
+// the fold: lane = value coordinate, warp = every eighth latent coordinate, summed in warp
+// order.
 template <typename W, typename O>
-__global__ void __launch_bounds__(LA_THREADS)
+__global__ void __launch_bounds__(LU_THREADS)
 latent_unfold_kernel(O* __restrict__ out, long out_ld, const float* __restrict__ lat,
                      const W* __restrict__ uvt, const float* __restrict__ gate, long gate_ld,
                      int n_tokens, int heads, int rank, int vdim) {
     extern __shared__ float ls[];                        // [LA_GROUP][rank]
+    __shared__ float part[LU_SLICES][LA_GROUP][LA_OUT];
     const int t0 = blockIdx.x * LA_GROUP, h = blockIdx.y;
     for (int e = threadIdx.x; e < LA_GROUP * rank; e += blockDim.x) {
         const int j = e / rank, r = e - j * rank;
         ls[e] = (t0 + j < n_tokens) ? lat[((size_t)(t0 + j) * heads + h) * rank + r] : 0.0f;
     }
     __syncthreads();
-    for (int v = threadIdx.x; v < vdim; v += blockDim.x) {
-        float acc[LA_GROUP];
+    const int lane = threadIdx.x & 31, slice = threadIdx.x >> 5;
+    const int v = blockIdx.z * LA_OUT + lane;
+    float acc[LA_GROUP];
 #pragma unroll
-        for (int j = 0; j < LA_GROUP; ++j) acc[j] = 0.0f;
+    for (int j = 0; j < LA_GROUP; ++j) acc[j] = 0.0f;
+    if (v < vdim) {
         const W* w = uvt + (size_t)h * rank * vdim + v;
-        for (int r = 0; r < rank; ++r) {
+#pragma unroll 16
+        for (int r = slice; r < rank; r += LU_SLICES) {
             const float wv = prb_to_float<W>(w[(size_t)r * vdim]);
 #pragma unroll
             for (int j = 0; j < LA_GROUP; ++j) acc[j] = fmaf(ls[j * rank + r], wv, acc[j]);
         }
+    }
 #pragma unroll
-        for (int j = 0; j < LA_GROUP; ++j) {
-            const int t = t0 + j;
-            if (t >= n_tokens) continue;
-            const float g = gate ? la_sigmoid(gate[(size_t)t * gate_ld + h]) : 1.0f;
-            out[(size_t)t * out_ld + h * vdim + v] = prb_from_float<O>(acc[j] * g);
-        }
+    for (int j = 0; j < LA_GROUP; ++j) part[slice][j][lane] = acc[j];
+    __syncthreads();
+    for (int e = threadIdx.x; e < LA_GROUP * LA_OUT; e += blockDim.x) {
+        const int j = e / LA_OUT, l = e - j * LA_OUT;
+        const int vv = blockIdx.z * LA_OUT + l, t = t0 + j;
+        if (t >= n_tokens || vv >= vdim) continue;
+        float sum = part[0][j][l];
+#pragma unroll
+        for (int sl = 1; sl < LU_SLICES; ++sl) sum += part[sl][j][l];
+        const float g = gate ? la_sigmoid(gate[(size_t)t * gate_ld + h]) : 1.0f;
+        out[(size_t)t * out_ld + h * vdim + vv] = prb_from_float<O>(sum * g);
     }
 }
 }  // namespace
@@ -293,7 +329,7 @@ PRB_API int prb_latent_fold(void* qa, const float* q, long ld, const void* uk,
         return PRB_E_SIZE;
     const size_t smem = (size_t)LA_GROUP * dim * sizeof(float);
     if (smem > 48 * 1024) return PRB_E_SIZE;
-    dim3 grid((n_tokens + LA_GROUP - 1) / LA_GROUP, heads);
+    dim3 grid((n_tokens + LA_GROUP - 1) / LA_GROUP, heads, (rank + LA_OUT - 1) / LA_OUT + 1);
     if (w_dtype == PRB_F32 && out_dtype == PRB_F32)
         latent_fold_kernel<float, float><<<grid, LA_THREADS, smem, stream>>>(
             (float*)qa, q, ld, (const float*)uk, positions, freq, n_tokens, heads, dim, rot_dim,
@@ -345,9 +381,9 @@ PRB_API int prb_latent_unfold(void* out, long out_ld, const float* lat, const vo
     if (heads <= 0 || heads > 65535 || rank <= 0 || vdim <= 0) return PRB_E_SIZE;
     const size_t smem = (size_t)LA_GROUP * rank * sizeof(float);
     if (smem > 48 * 1024) return PRB_E_SIZE;
-    dim3 grid((n_tokens + LA_GROUP - 1) / LA_GROUP, heads);
+    dim3 grid((n_tokens + LA_GROUP - 1) / LA_GROUP, heads, (vdim + LA_OUT - 1) / LA_OUT);
 #define PRB_LU(W, O)                                                                      \
-    latent_unfold_kernel<W, O><<<grid, LA_THREADS, smem, stream>>>(                       \
+    latent_unfold_kernel<W, O><<<grid, LU_THREADS, smem, stream>>>(                       \
         (O*)out, out_ld, lat, (const W*)uvt, gate, gate_ld, n_tokens, heads, rank, vdim)
     if (w_dtype == PRB_F32 && out_dtype == PRB_F32) PRB_LU(float, float);
     else if (w_dtype == PRB_BF16 && out_dtype == PRB_BF16) PRB_LU(__nv_bfloat16, __nv_bfloat16);

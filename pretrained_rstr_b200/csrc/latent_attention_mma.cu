@@ -7,23 +7,24 @@
 // keys brought to shared memory once serves them all, as key and as value.
 //
 // One CTA = one work item (some consecutive tokens of a request, all heads) x one range of
-// keys (a multiple of 64 absolute positions).  Its four warps are 4 / kw row tiles of 16 rows
+// keys (a multiple of 64 absolute positions).  Its warps are WARPS / kw row tiles of 16 rows
 // times kw parts of every key block:
-//   kw = 1  prompt portions: 64 rows, each warp walks all keys for its 16 rows
-//   kw = 4  single tokens with up to 16 heads: the warps share the rows and split the keys
+//   kw = 1, 8 warps  prompt portions: 128 rows, each warp walks all keys for its 16 rows
+//   kw = 4, 4 warps  single tokens with up to 16 heads: the warps share the rows and split
+//                    the keys; their results are joined in shared memory (warp order)
 // S = Q K^T and O += P V are mma.sync m16n8k16; Q and K fragments come by ldmatrix, V fragments
 // by ldmatrix.trans from the same rows, P stays in registers.  Key blocks are double
-// buffered with cp.async.  Every (warp's key part) x (key range) leaves a partial result
-// (running maximum, sum, unnormalised rows) in a workspace; prb_latent_merge joins a row's
-// partials in a fixed order, adds the optional sink to the denominator and normalises.
+// buffered with cp.async.  Every key range leaves a partial result (running maximum, sum,
+// unnormalised rows) in a workspace; a second kernel joins a row's partials in a fixed
+// order, adds the optional sink to the denominator and normalises.
 // Which keys meet in which partial depends on absolute positions only, so a row's result
 // does not depend on the rest of the batch.
 #include "common.cuh"
 
 namespace {
-constexpr int LM_THREADS = 128;
-constexpr int LM_ROWS = 64;
+constexpr int LM_ROWS = 128;         // most rows of a work item (8 warps, kw = 1)
 constexpr int LM_KEYS = 64;
+constexpr int LM_MAX_PARTS = 32;     // most key ranges of a row (a lane each in the join)
 
 struct LmArgs {
     const __nv_bfloat16* qa;      // [T, heads, D]
@@ -34,6 +35,8 @@ struct LmArgs {
     const int* item_row0;         // first token row of every item
     const int* item_tokens;       // tokens of every item, or null: one each
     const int* item_count;        // device-side count, or null
+    float* out;                   // [T, heads, rank]: written here when a row has one key range
+    const float* sinks;           // [heads] or null
     float* ws_o;                  // [(item * ws_rows + row) * parts + part][rank]
     float* ws_ml;                 // [(item * ws_rows + row) * parts + part][2]
     int ws_rows;                  // rows an item has room for in the workspace
@@ -75,14 +78,27 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<const uint32_t*>(&v);
 }
 
+// What a row's unnormalised sums are multiplied by when its keys were one range: 1 over the
+// softmax's denominator, which also holds exp(sink) when the head has a sink.
+__device__ __forceinline__ float lm_finish(float m, float l, const float* sinks, int h) {
+    const float sk = sinks ? sinks[h] : -INFINITY;
+    const float top = fmaxf(m, sk);
+    if (top == -INFINITY) return 0.0f;
+    const float f = (m == -INFINITY) ? 0.0f : expf(m - top);
+    const float denom = l * f + (sinks ? expf(sk - top) : 0.0f);
+    return denom > 0.0f ? f / denom : 0.0f;
+}
+
 // NT_O: value tiles of 8 coordinates a warp accumulates (rank <= 8 * NT_O).
-template <int NT_O>
-__global__ void __launch_bounds__(LM_THREADS)
+template <int NT_O, int WARPS>
+__global__ void __launch_bounds__(32 * WARPS)
 latent_mma_kernel(LmArgs a) {
+    constexpr int LM_THREADS = 32 * WARPS;
     extern __shared__ __align__(16) unsigned char lm_smem[];
     const int D = a.rank + a.rot_dim, LD = D + 8;         // (+8: rows 16 bytes apart in the banks)
+    const int q_rows = 16 * WARPS / a.kw;                 // rows of the item's tile
     __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(lm_smem);
-    __nv_bfloat16* kbuf[2] = {qs + LM_ROWS * LD, qs + 2 * LM_ROWS * LD};
+    __nv_bfloat16* kbuf[2] = {qs + q_rows * LD, qs + (q_rows + LM_KEYS) * LD};
     const int item = blockIdx.x, split = blockIdx.y;
     if (item >= a.n_items || (a.item_count != nullptr && item >= *a.item_count)) return;
     const int t0 = a.item_row0[item];
@@ -101,7 +117,7 @@ latent_mma_kernel(LmArgs a) {
     const int k_end = min(k_begin + a.split_keys, pos_max + 1);
     const int lo_min = a.window > 0 ? max(0, pos0 - a.window + 1) : 0;
     const int kb_first = max(k_begin, lo_min) / LM_KEYS * LM_KEYS;
-    const int nrows = min(min(ntok * a.heads, LM_ROWS), a.ws_rows);
+    const int nrows = min(min(ntok * a.heads, q_rows), a.ws_rows);
     const int* table = a.block_table + (size_t)b * a.max_pages;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, tg = lane & 3;
     const int chunks = D / 8;                              // 16-byte pieces of a row
@@ -109,28 +125,30 @@ latent_mma_kernel(LmArgs a) {
     // the queries of the item: rows t0 * heads .. of qa, contiguous
     {
         const __nv_bfloat16* src = a.qa + (size_t)t0 * a.heads * D;
-        for (int c = tid; c < LM_ROWS * chunks; c += LM_THREADS) {
+        for (int c = tid; c < q_rows * chunks; c += LM_THREADS) {
             const int r = c / chunks, k = c - r * chunks;
             cp_async16(qs + r * LD + k * 8, src + (size_t)r * D + k * 8, r < nrows);
         }
     }
+    // a thread copies pieces of ONE key row of a block: one look-up in the block table, then
+    // copies that do not wait for one another
+    constexpr int TPR = LM_THREADS / LM_KEYS;              // threads per key row
+    const int lrow = tid / TPR, lsub = tid - lrow * TPR;
     auto load_keys = [&](int kb, __nv_bfloat16* dst) {
-        for (int c = tid; c < LM_KEYS * chunks; c += LM_THREADS) {
-            const int r = c / chunks, k = c - r * chunks;
-            const int j = kb + r;
-            bool ok = j < k_end;
-            const __nv_bfloat16* src = a.cache;
-            if (ok) {
-                const int page = table[j / a.page_size];
-                if (page < 0 || page >= a.num_pages) {
-                    if (k == 0 && j >= lo_min) prb_set_status(a.status, PRB_S_PAGE_RANGE, t0, j, page);
-                    ok = false;
-                } else {
-                    src = a.cache + ((size_t)page * a.page_size + (j % a.page_size)) * D + k * 8;
-                }
+        const int j = kb + lrow;
+        bool ok = j < k_end;
+        const __nv_bfloat16* src = a.cache;
+        if (ok) {
+            const int page = table[j / a.page_size];
+            if (page < 0 || page >= a.num_pages) {
+                if (lsub == 0 && j >= lo_min) prb_set_status(a.status, PRB_S_PAGE_RANGE, t0, j, page);
+                ok = false;
+            } else {
+                src = a.cache + ((size_t)page * a.page_size + (j % a.page_size)) * D;
             }
-            cp_async16(dst + r * LD + k * 8, src, ok);
         }
+        for (int k = lsub; k < chunks; k += TPR)
+            cp_async16(dst + lrow * LD + k * 8, ok ? src + k * 8 : src, ok);
     };
     load_keys(kb_first, kbuf[0]);
     cp_async_commit();
@@ -246,41 +264,114 @@ latent_mma_kernel(LmArgs a) {
         __syncthreads();                                   // the buffer may be filled again
     }
     cp_async_wait<0>();
-    if (!active) return;
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
     l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
-    const int part = split * kw + kq;
+    if (kw > 1) {
+        // the kw warps of a row tile hold the same rows over different keys: joined in warp
+        // order through the key buffers, once every thread's copies into them have landed
+        __syncthreads();
+        float* red_ml = reinterpret_cast<float*>(kbuf[0]);           // [WARPS][16][2]
+        float* red_f = red_ml + WARPS * 16 * 2;                       // [WARPS][16]
+        float* red_o = red_f + WARPS * 16;                            // [WARPS][16][rank]
+        if (tg == 0) {
+            red_ml[(warp * 16 + g) * 2] = m0;
+            red_ml[(warp * 16 + g) * 2 + 1] = l0;
+            red_ml[(warp * 16 + g + 8) * 2] = m1;
+            red_ml[(warp * 16 + g + 8) * 2 + 1] = l1;
+        }
+#pragma unroll
+        for (int nt = 0; nt < NT_O; ++nt) {
+            const int d = nt * 8 + 2 * tg;
+            if (d < a.rank) {
+                *reinterpret_cast<float2*>(red_o + (size_t)(warp * 16 + g) * a.rank + d) =
+                    make_float2(o[nt][0], o[nt][1]);
+                *reinterpret_cast<float2*>(red_o + (size_t)(warp * 16 + g + 8) * a.rank + d) =
+                    make_float2(o[nt][2], o[nt][3]);
+            }
+        }
+        __syncthreads();
+        const int tiles = WARPS / kw;
+        for (int e = tid; e < tiles * 16; e += LM_THREADS) {
+            const int tile = e / 16, r = e - tile * 16;
+            float top = -INFINITY;
+            for (int w = 0; w < kw; ++w) top = fmaxf(top, red_ml[((tile * kw + w) * 16 + r) * 2]);
+            float sum = 0.0f;
+            for (int w = 0; w < kw; ++w) {
+                const float mw = red_ml[((tile * kw + w) * 16 + r) * 2];
+                const float f = (mw == -INFINITY) ? 0.0f : expf(mw - top);
+                red_f[(tile * kw + w) * 16 + r] = f;
+                sum += red_ml[((tile * kw + w) * 16 + r) * 2 + 1] * f;
+            }
+            const int row = tile * 16 + r;
+            if (row < nrows) {
+                if (a.parts == 1) {                       // the only range: normalise here
+                    const float fin = lm_finish(top, sum, a.sinks, row % a.heads);
+                    for (int w = 0; w < kw; ++w) red_f[(tile * kw + w) * 16 + r] *= fin;
+                } else {
+                    const size_t slot = ((size_t)item * a.ws_rows + row) * a.parts + split;
+                    a.ws_ml[slot * 2] = top;
+                    a.ws_ml[slot * 2 + 1] = sum;
+                }
+            }
+        }
+        __syncthreads();
+        for (int e = tid; e < tiles * 16 * a.rank; e += LM_THREADS) {
+            const int row = e / a.rank, d = e - row * a.rank;
+            if (row >= nrows) continue;
+            const int tile = row / 16, r = row - tile * 16;
+            float acc = 0.0f;
+            for (int w = 0; w < kw; ++w)
+                acc += red_o[(size_t)((tile * kw + w) * 16 + r) * a.rank + d] *
+                       red_f[(tile * kw + w) * 16 + r];
+            if (a.parts == 1)
+                a.out[((size_t)t0 * a.heads + row) * a.rank + d] = acc;
+            else
+                a.ws_o[(((size_t)item * a.ws_rows + row) * a.parts + split) * a.rank + d] = acc;
+        }
+        return;
+    }
+    if (!active) return;
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
         const int row = half ? row1 : row0;
         if (row >= nrows) continue;
-        const size_t slot = ((size_t)item * a.ws_rows + row) * a.parts + part;
-        if (tg == 0) {
-            a.ws_ml[slot * 2] = half ? m1 : m0;
-            a.ws_ml[slot * 2 + 1] = half ? l1 : l0;
+        float* dst;
+        float fin = 1.0f;
+        if (a.parts == 1) {                               // the only range: normalise here
+            fin = lm_finish(half ? m1 : m0, half ? l1 : l0, a.sinks, row % a.heads);
+            dst = a.out + ((size_t)t0 * a.heads + row) * a.rank;
+        } else {
+            const size_t slot = ((size_t)item * a.ws_rows + row) * a.parts + split;
+            if (tg == 0) {
+                a.ws_ml[slot * 2] = half ? m1 : m0;
+                a.ws_ml[slot * 2 + 1] = half ? l1 : l0;
+            }
+            dst = a.ws_o + slot * a.rank;
         }
-        float* dst = a.ws_o + slot * a.rank;
 #pragma unroll
         for (int nt = 0; nt < NT_O; ++nt) {
             const int d = nt * 8 + 2 * tg;
             if (d < a.rank)
                 *reinterpret_cast<float2*>(dst + d) =
-                    half ? make_float2(o[nt][2], o[nt][3]) : make_float2(o[nt][0], o[nt][1]);
+                    half ? make_float2(o[nt][2] * fin, o[nt][3] * fin)
+                         : make_float2(o[nt][0] * fin, o[nt][1] * fin);
         }
     }
 }
 
-// grid (items * ws_rows): one CTA per (item, row); joins the row's partials in order.
+// One warp per (item, row): joins the row's partial results in order.  Lane p holds part p's
+// maximum and sum; the denominator also takes the head's sink.
 __global__ void __launch_bounds__(128)
 latent_merge_kernel(float* __restrict__ out, const float* __restrict__ ws_o,
                     const float* __restrict__ ws_ml, const int* __restrict__ item_row0,
                     const int* __restrict__ item_tokens, const int* __restrict__ item_count,
                     const int* __restrict__ seq_of_token, const int* __restrict__ positions,
                     const float* __restrict__ sinks, int n_items, int heads, int rank, int parts,
-                    int kw, int split_keys, int ws_rows) {
-    const int item = blockIdx.x / ws_rows, row = blockIdx.x % ws_rows;
+                    int split_keys, int ws_rows) {
+    const int unit = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    const int item = unit / ws_rows, row = unit - item * ws_rows;
     if (item >= n_items || (item_count != nullptr && item >= *item_count)) return;
     const int ntok = item_tokens ? item_tokens[item] : 1;
     if (row >= ntok * heads) return;
@@ -288,25 +379,33 @@ latent_merge_kernel(float* __restrict__ out, const float* __restrict__ ws_o,
     float* o = out + ((size_t)t * heads + h) * rank;
     const int pos = positions[t];
     if (seq_of_token[t] < 0 || pos < 0) {
-        for (int d = threadIdx.x; d < rank; d += blockDim.x) o[d] = 0.0f;
+        for (int d = lane; d < rank; d += 32) o[d] = 0.0f;
         return;
     }
-    const int n = min(parts, (pos / split_keys + 1) * kw);
+    const int n = min(parts, pos / split_keys + 1);
     const size_t base = ((size_t)item * ws_rows + row) * parts;
-    float top = sinks ? sinks[h] : -INFINITY;
-    for (int p = 0; p < n; ++p) top = fmaxf(top, ws_ml[(base + p) * 2]);
-    float denom = sinks ? expf(sinks[h] - top) : 0.0f;
-    for (int p = 0; p < n; ++p) {
-        const float m = ws_ml[(base + p) * 2];
-        if (m != -INFINITY) denom += ws_ml[(base + p) * 2 + 1] * expf(m - top);
-    }
-    for (int d = threadIdx.x; d < rank; d += blockDim.x) {
+    const float m = lane < n ? ws_ml[(base + lane) * 2] : -INFINITY;
+    const float l = lane < n ? ws_ml[(base + lane) * 2 + 1] : 0.0f;
+    const float sk = sinks ? sinks[h] : -INFINITY;
+    const float top = fmaxf(prb_warp_max(m), sk);
+    const float f = (m == -INFINITY) ? 0.0f : expf(m - top);
+    const float denom = prb_warp_sum(l * f) + (sinks ? expf(sk - top) : 0.0f);
+    const float inv = denom > 0.0f ? 1.0f / denom : 0.0f;
+    for (int d0 = 0; d0 < rank; d0 += 32) {
+        const int d = d0 + lane;
         float acc = 0.0f;
-        for (int p = 0; p < n; ++p) {
-            const float m = ws_ml[(base + p) * 2];
-            if (m != -INFINITY) acc += ws_o[(base + p) * rank + d] * expf(m - top);
+        for (int p0 = 0; p0 < n; p0 += 8) {               // eight parts' loads in flight at once
+            float v[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                v[i] = (p0 + i < n && d < rank) ? ws_o[(base + p0 + i) * rank + d] : 0.0f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float fp = __shfl_sync(0xffffffffu, f, (p0 + i) & 31);
+                if (p0 + i < n && fp != 0.0f) acc = fmaf(v[i], fp, acc);
+            }
         }
-        o[d] = denom > 0.0f ? acc / denom : 0.0f;
+        if (d < rank) o[d] = acc * inv;
     }
 }
 }  // namespace
@@ -315,13 +414,14 @@ PRB_API int prb_latent_mma_supports(int heads, int rank, int rot_dim) {
     if (heads <= 0 || heads > LM_ROWS || rank <= 0 || rank > 256 || rank % 16 != 0 || rot_dim < 0 ||
         rot_dim % 16 != 0)
         return 0;
-    const size_t smem = (size_t)3 * LM_ROWS * (rank + rot_dim + 8) * sizeof(__nv_bfloat16);
-    return smem <= 200 * 1024 ? 1 : 0;
+    const size_t smem = (size_t)(LM_ROWS + 2 * LM_KEYS) * (rank + rot_dim + 8) * sizeof(__nv_bfloat16);
+    return smem <= 220 * 1024 ? 1 : 0;
 }
 
 // How the warps of a CTA share single tokens: the key parts per block (4, 2 or 1).
 PRB_API int prb_latent_mma_single_kw(int heads) { return heads <= 16 ? 4 : (heads <= 32 ? 2 : 1); }
 PRB_API int prb_latent_mma_rows() { return LM_ROWS; }
+PRB_API int prb_latent_mma_max_splits() { return LM_MAX_PARTS; }
 
 PRB_API int prb_latent_attention_mma(float* out, const void* qa, const void* cache,
                                      const int* block_table, const int* seq_of_token,
@@ -332,35 +432,46 @@ PRB_API int prb_latent_attention_mma(float* out, const void* qa, const void* cac
                                      int num_pages, float scale, int window, int split_keys,
                                      int splits, int kw, int ws_rows, int* status,
                                      cudaStream_t stream) {
+    // kw = 1: 8 warps, up to 128 rows an item; kw = 4 or 2: 4 warps, 16 or 32 rows
+    const int warps = kw == 1 ? 8 : 4;
+    const int q_rows = 16 * warps / (kw > 0 ? kw : 1);
     if (n_items <= 0) return 0;
     if (!prb_latent_mma_supports(heads, rank, rot_dim) || page_size <= 0 || max_pages <= 0 ||
         split_keys <= 0 || split_keys % LM_KEYS != 0 || splits <= 0 || splits > 65535 ||
-        (kw != 1 && kw != 2 && kw != 4) || ws_rows <= 0 || ws_rows > LM_ROWS ||
-        (item_tokens == nullptr && heads > ws_rows) || (kw > 1 && heads > 16 * (4 / kw)))
+        (kw != 1 && kw != 2 && kw != 4) || ws_rows <= 0 || ws_rows > q_rows ||
+        (item_tokens == nullptr && heads > ws_rows) || heads > q_rows || splits > LM_MAX_PARTS)
         return PRB_E_SIZE;
     if (((uintptr_t)qa) % 16 != 0 || ((uintptr_t)cache) % 16 != 0) return PRB_E_ALIGN;
     LmArgs a{(const __nv_bfloat16*)qa, (const __nv_bfloat16*)cache, block_table, seq_of_token,
-             positions, item_row0, item_tokens, item_count, ws_o, ws_ml, ws_rows, n_items, heads, rank,
-             rot_dim, page_size, max_pages, num_pages, window, split_keys, splits * kw, kw, scale,
+             positions, item_row0, item_tokens, item_count, out, sinks, ws_o, ws_ml, ws_rows, n_items,
+             heads, rank,
+             rot_dim, page_size, max_pages, num_pages, window, split_keys, splits, kw, scale,
              status};
-    const size_t smem = (size_t)3 * LM_ROWS * (rank + rot_dim + 8) * sizeof(__nv_bfloat16);
+    const size_t smem = (size_t)(q_rows + 2 * LM_KEYS) * (rank + rot_dim + 8) * sizeof(__nv_bfloat16);
     dim3 grid(n_items, splits);
-#define PRB_LM(NT)                                                                              \
+#define PRB_LM(NT, W)                                                                           \
     do {                                                                                        \
         if (smem > 48 * 1024)                                                                   \
-            cudaFuncSetAttribute(latent_mma_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
-                                 (int)smem);                                                    \
-        latent_mma_kernel<NT><<<grid, LM_THREADS, smem, stream>>>(a);                           \
+            cudaFuncSetAttribute(latent_mma_kernel<NT, W>,                                      \
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);       \
+        latent_mma_kernel<NT, W><<<grid, 32 * W, smem, stream>>>(a);                            \
     } while (0)
-    if (rank <= 64) PRB_LM(8);
-    else if (rank <= 128) PRB_LM(16);
-    else if (rank <= 192) PRB_LM(24);
-    else PRB_LM(32);
+#define PRB_LM_RANK(W)                   \
+    do {                                 \
+        if (rank <= 64) PRB_LM(8, W);    \
+        else if (rank <= 128) PRB_LM(16, W); \
+        else if (rank <= 192) PRB_LM(24, W); \
+        else PRB_LM(32, W);              \
+    } while (0)
+    if (warps == 8) PRB_LM_RANK(8);
+    else PRB_LM_RANK(4);
+#undef PRB_LM_RANK
 #undef PRB_LM
     PRB_LAUNCH_CHECK();
-    latent_merge_kernel<<<n_items * ws_rows, 128, 0, stream>>>(
+    if (splits == 1) return 0;                 // every row had one range and is finished
+    latent_merge_kernel<<<(n_items * ws_rows + 3) / 4, 128, 0, stream>>>(
         out, ws_o, ws_ml, item_row0, item_tokens, item_count, seq_of_token, positions, sinks,
-        n_items, heads, rank, splits * kw, kw, split_keys, ws_rows);
+        n_items, heads, rank, splits, split_keys, ws_rows);
     PRB_LAUNCH_CHECK();
     return 0;
 }

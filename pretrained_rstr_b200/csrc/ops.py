@@ -1043,12 +1043,13 @@ def latent_attention_mma(out, qa, cache, block_table, seq_of_token, positions, i
                          status) -> None:
     """The same as ``latent_attention`` on tensor cores for bfloat16 queries and cache.  Work
     items: item i is ``item_tokens[i]`` (1 if None) consecutive tokens of one request from
-    token row ``item_row0[i]`` on, all heads (heads * tokens <= ``ws_rows`` <= 64); ``n_items``
+    token row ``item_row0[i]`` on, all heads (heads * tokens <= ``ws_rows`` <= 128); ``n_items``
     are launched, ``item_count`` (device int32, or None) bounds them.  Keys go in ``splits``
     ranges of ``split_keys`` positions (a multiple of 64) to a CTA each, whose warps split every
-    block of 64 keys ``kw`` ways (1: prompt portions; 4 or 2: single tokens of up to 16 or 32
-    heads).  ``ws_o`` float32 [n_items * ws_rows * splits * kw * rank] and ``ws_ml`` (the same
-    without rank, times 2) hold the partial results a second kernel joins into ``out``."""
+    block of 64 keys ``kw`` ways (1: prompt portions, items of up to 128 rows; 4 or 2: single
+    tokens of up to 16 or 32 heads).  ``ws_o`` float32 [n_items * ws_rows * splits * rank] and
+    ``ws_ml`` (the same without rank, times 2) hold the partial results of the key ranges,
+    which a second kernel joins into ``out``."""
     what = "latent_attention_mma"
     _need(out, torch.float32, "out", what)
     _need(qa, torch.bfloat16, "qa", what)
@@ -1062,7 +1063,7 @@ def latent_attention_mma(out, qa, cache, block_table, seq_of_token, positions, i
         _need(item_tokens, torch.int32, "item_tokens", what)
     if item_row0.numel() < n_items or (item_tokens is not None and item_tokens.numel() < n_items):
         raise KernelArgumentError(f"{what}: the work list is shorter than {n_items} items")
-    parts = int(splits) * int(kw)
+    parts = int(splits)
     _need(ws_o, torch.float32, "ws_o", what)
     _need(ws_ml, torch.float32, "ws_ml", what)
     if ws_o.numel() < n_items * ws_rows * parts * rank or ws_ml.numel() < n_items * ws_rows * parts * 2:
@@ -1075,5 +1076,5 @@ def latent_attention_mma(out, qa, cache, block_table, seq_of_token, positions, i
         d - rank, page_size, block_table.shape[1], num_pages, float(scale), int(window or 0),
         int(split_keys), int(splits), int(kw), int(ws_rows), _p(status), _stream())
     _check(code, what)
-    if code == 0 and n_items > 0:
+    if code == 0 and n_items > 0 and splits > 1:
         add_launches(1)                      # the kernel that joins the partial results

@@ -85,11 +85,11 @@ class FusedInput:
 class LatentWork(WorkPlanner):
     """How the tensor-core kernel cuts a step.  A request that brings one token is a
     "single": an item of its own whose CTAs split the keys.  A portion of a prompt goes in
-    "tiles" of consecutive tokens, as many as fit a CTA's 64 (token, head) rows: 64 // heads,
+    "tiles" of consecutive tokens, as many as fit a CTA's 128 (token, head) rows: 128 // heads,
     so mixers with other head counts have lists of their own (``tile_row0_<tokens>``)."""
 
     key = "latent_attention"
-    ROWS = 64
+    ROWS = 128
 
     def __init__(self):
         self.tile_tokens = set()           # tokens per tile of the mixers that use the lists
@@ -148,10 +148,10 @@ class LatentWork(WorkPlanner):
 
 def key_splits(items: int, max_context: int, most: int, sm_count: int):
     """(keys per range, ranges) for a launch of ``items`` work items over contexts of up to
-    ``max_context`` keys: about two CTAs per SM, ranges of whole 64-key blocks, at least four
+    ``max_context`` keys: about two CTAs per SM, ranges of whole 64-key blocks, at least two
     blocks long unless the context is shorter."""
     blocks = max(1, -(-max_context // 64))
-    wanted = max(1, min(most, -(-2 * sm_count // max(1, items)), max(1, blocks // 4)))
+    wanted = max(1, min(most, -(-2 * sm_count // max(1, items)), max(1, blocks // 2)))
     split_keys = -(-blocks // wanted) * 64
     return split_keys, -(-blocks * 64 // split_keys)
 
@@ -251,7 +251,7 @@ class LatentAttention(Mixer):
 
 
     #: most key ranges of a launch: single tokens, prompt tiles
-    MAX_SPLITS = (16, 8)
+    MAX_SPLITS = (32, 8)
 
     def _attend_tensor_cores(self, ctx, lat, qa, cache: LayerCache, group) -> None:
         """Single tokens and prompt tiles as two launches (each only if the step has such
@@ -271,7 +271,7 @@ class LatentAttention(Mixer):
             n = cap if count is None else count
             most = max(1, min(most, 2 * self.sm_count // cap))     # (bounds the workspace too)
             split_keys, splits = key_splits(n, ctx.max_context, most, self.sm_count)
-            slots = cap * ws_rows * most * kw
+            slots = cap * ws_rows * most
             ws_o = ctx.scratch("latent_part_o", (slots * self.rank,), torch.float32)
             ws_ml = ctx.scratch("latent_part_ml", (slots * 2,), torch.float32)
             ops.latent_attention_mma(

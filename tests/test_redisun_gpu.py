@@ -293,11 +293,11 @@ class LatentCase:
             queries = [(b, p, q.to(torch.bfloat16).float()) for b, p, q in queries]
             kw = ops.latent_mma_single_kw(heads) if kernel == "single" else 1
             items = items or [(i, 1) for i in range(n)]
-            ws_rows = heads if kernel == "single" else 64
+            ws_rows = heads if kernel == "single" else 128
             longest = max(p for _, p, _ in queries) + 1
             split_keys = split_keys or 128
             splits = -(-longest // split_keys)
-            slots = (len(items) + 2) * ws_rows * splits * kw
+            slots = (len(items) + 2) * ws_rows * splits
             ws_o = torch.full((slots * self.rank,), float("nan"), device=DEV)
             ws_ml = torch.full((slots * 2,), float("nan"), device=DEV)
             count = i32([len(items)])
@@ -339,14 +339,14 @@ def test_latent_attention_random(dtype, kernel):
 @pytest.mark.parametrize("heads,rank,rot", [(3, 48, 16), (8, 128, 32), (12, 256, 32), (20, 64, 0),
                                             (40, 32, 16)])
 def test_latent_attention_tiles_of_a_portion(heads, rank, rot):
-    """A portion of consecutive tokens as the tensor-core kernel's tiles of 64 // heads
+    """A portion of consecutive tokens as the tensor-core kernel's tiles of 128 // heads
     tokens, the keys in ranges of several sizes; and the same tokens one by one."""
     case = LatentCase([700, 90], rank, rot, torch.bfloat16, seed=13).to_device()
     g = torch.Generator().manual_seed(14)
     first, n = 381, 150
     queries = [(0, first + i, torch.randn(heads, rank + rot, generator=g)) for i in range(n)]
     queries += [(1, 20 + i, torch.randn(heads, rank + rot, generator=g)) for i in range(70)]
-    tq = 64 // heads
+    tq = 128 // heads
     items = [(r0, min(tq, n - r0)) for r0 in range(0, n, tq)]
     items += [(n + r0, min(tq, 70 - r0)) for r0 in range(0, 70, tq)]
     sinks = torch.randn(heads, generator=g)
