@@ -36,6 +36,9 @@ struct LmArgs {
     const int* item_tokens;       // tokens of every item, or null: one each
     const int* item_count;        // device-side count, or null
     float* out;                   // [T, heads, rank]: written here when a row has one key range
+    __nv_bfloat16* out_bf;        // instead of out: bfloat16, times sigmoid(gate[t, h])
+    const float* gate;            // [T, gate_ld], head h at column h; or null
+    long gate_ld;
     const float* sinks;           // [heads] or null
     float* ws_o;                  // [(item * ws_rows + row) * parts + part][rank]
     float* ws_ml;                 // [(item * ws_rows + row) * parts + part][2]
@@ -87,6 +90,12 @@ __device__ __forceinline__ float lm_finish(float m, float l, const float* sinks,
     const float f = (m == -INFINITY) ? 0.0f : expf(m - top);
     const float denom = l * f + (sinks ? expf(sk - top) : 0.0f);
     return denom > 0.0f ? f / denom : 0.0f;
+}
+
+// The factor of a finished row's gate (1 without one), and the store of finished numbers in
+// the output's type.
+__device__ __forceinline__ float lm_gate(const float* gate, long gate_ld, int t, int h) {
+    return gate ? 1.0f / (1.0f + expf(-gate[(size_t)t * gate_ld + h])) : 1.0f;
 }
 
 // NT_O: value tiles of 8 coordinates a warp accumulates (rank <= 8 * NT_O).
@@ -307,7 +316,8 @@ latent_mma_kernel(LmArgs a) {
             const int row = tile * 16 + r;
             if (row < nrows) {
                 if (a.parts == 1) {                       // the only range: normalise here
-                    const float fin = lm_finish(top, sum, a.sinks, row % a.heads);
+                    float fin = lm_finish(top, sum, a.sinks, row % a.heads);
+                    if (a.out_bf) fin *= lm_gate(a.gate, a.gate_ld, t0 + row / a.heads, row % a.heads);
                     for (int w = 0; w < kw; ++w) red_f[(tile * kw + w) * 16 + r] *= fin;
                 } else {
                     const size_t slot = ((size_t)item * a.ws_rows + row) * a.parts + split;
@@ -325,7 +335,9 @@ latent_mma_kernel(LmArgs a) {
             for (int w = 0; w < kw; ++w)
                 acc += red_o[(size_t)((tile * kw + w) * 16 + r) * a.rank + d] *
                        red_f[(tile * kw + w) * 16 + r];
-            if (a.parts == 1)
+            if (a.parts == 1 && a.out_bf)
+                a.out_bf[((size_t)t0 * a.heads + row) * a.rank + d] = __float2bfloat16_rn(acc);
+            else if (a.parts == 1)
                 a.out[((size_t)t0 * a.heads + row) * a.rank + d] = acc;
             else
                 a.ws_o[(((size_t)item * a.ws_rows + row) * a.parts + split) * a.rank + d] = acc;
@@ -337,10 +349,23 @@ latent_mma_kernel(LmArgs a) {
     for (int half = 0; half < 2; ++half) {
         const int row = half ? row1 : row0;
         if (row >= nrows) continue;
-        float* dst;
+        float* dst = nullptr;
         float fin = 1.0f;
         if (a.parts == 1) {                               // the only range: normalise here
             fin = lm_finish(half ? m1 : m0, half ? l1 : l0, a.sinks, row % a.heads);
+            if (a.out_bf) {
+                fin *= lm_gate(a.gate, a.gate_ld, t0 + row / a.heads, row % a.heads);
+                __nv_bfloat16* bdst = a.out_bf + ((size_t)t0 * a.heads + row) * a.rank;
+#pragma unroll
+                for (int nt = 0; nt < NT_O; ++nt) {
+                    const int d = nt * 8 + 2 * tg;
+                    if (d < a.rank)
+                        *reinterpret_cast<__nv_bfloat162*>(bdst + d) =
+                            half ? __floats2bfloat162_rn(o[nt][2] * fin, o[nt][3] * fin)
+                                 : __floats2bfloat162_rn(o[nt][0] * fin, o[nt][1] * fin);
+                }
+                continue;
+            }
             dst = a.out + ((size_t)t0 * a.heads + row) * a.rank;
         } else {
             const size_t slot = ((size_t)item * a.ws_rows + row) * a.parts + split;
@@ -364,7 +389,8 @@ latent_mma_kernel(LmArgs a) {
 // One warp per (item, row): joins the row's partial results in order.  Lane p holds part p's
 // maximum and sum; the denominator also takes the head's sink.
 __global__ void __launch_bounds__(128)
-latent_merge_kernel(float* __restrict__ out, const float* __restrict__ ws_o,
+latent_merge_kernel(float* __restrict__ out, __nv_bfloat16* __restrict__ out_bf,
+                    const float* __restrict__ gate, long gate_ld, const float* __restrict__ ws_o,
                     const float* __restrict__ ws_ml, const int* __restrict__ item_row0,
                     const int* __restrict__ item_tokens, const int* __restrict__ item_count,
                     const int* __restrict__ seq_of_token, const int* __restrict__ positions,
@@ -376,10 +402,13 @@ latent_merge_kernel(float* __restrict__ out, const float* __restrict__ ws_o,
     const int ntok = item_tokens ? item_tokens[item] : 1;
     if (row >= ntok * heads) return;
     const int t = item_row0[item] + row / heads, h = row % heads;
-    float* o = out + ((size_t)t * heads + h) * rank;
+    float* o = out ? out + ((size_t)t * heads + h) * rank : nullptr;
+    __nv_bfloat16* ob = out_bf ? out_bf + ((size_t)t * heads + h) * rank : nullptr;
     const int pos = positions[t];
     if (seq_of_token[t] < 0 || pos < 0) {
-        for (int d = lane; d < rank; d += 32) o[d] = 0.0f;
+        for (int d = lane; d < rank; d += 32) {
+            if (ob) ob[d] = __float2bfloat16_rn(0.0f); else o[d] = 0.0f;
+        }
         return;
     }
     const int n = min(parts, pos / split_keys + 1);
@@ -390,7 +419,8 @@ latent_merge_kernel(float* __restrict__ out, const float* __restrict__ ws_o,
     const float top = fmaxf(prb_warp_max(m), sk);
     const float f = (m == -INFINITY) ? 0.0f : expf(m - top);
     const float denom = prb_warp_sum(l * f) + (sinks ? expf(sk - top) : 0.0f);
-    const float inv = denom > 0.0f ? 1.0f / denom : 0.0f;
+    float inv = denom > 0.0f ? 1.0f / denom : 0.0f;
+    if (ob) inv *= lm_gate(gate, gate_ld, t, h);
     for (int d0 = 0; d0 < rank; d0 += 32) {
         const int d = d0 + lane;
         float acc = 0.0f;
@@ -405,7 +435,9 @@ latent_merge_kernel(float* __restrict__ out, const float* __restrict__ ws_o,
                 if (p0 + i < n && fp != 0.0f) acc = fmaf(v[i], fp, acc);
             }
         }
-        if (d < rank) o[d] = acc * inv;
+        if (d < rank) {
+            if (ob) ob[d] = __float2bfloat16_rn(acc * inv); else o[d] = acc * inv;
+        }
     }
 }
 }  // namespace
@@ -423,7 +455,8 @@ PRB_API int prb_latent_mma_single_kw(int heads) { return heads <= 16 ? 4 : (head
 PRB_API int prb_latent_mma_rows() { return LM_ROWS; }
 PRB_API int prb_latent_mma_max_splits() { return LM_MAX_PARTS; }
 
-PRB_API int prb_latent_attention_mma(float* out, const void* qa, const void* cache,
+PRB_API int prb_latent_attention_mma(float* out, void* out_bf, const float* gate, long gate_ld,
+                                     const void* qa, const void* cache,
                                      const int* block_table, const int* seq_of_token,
                                      const int* positions, const int* item_row0,
                                      const int* item_tokens, const int* item_count, int n_items,
@@ -442,8 +475,10 @@ PRB_API int prb_latent_attention_mma(float* out, const void* qa, const void* cac
         (item_tokens == nullptr && heads > ws_rows) || heads > q_rows || splits > LM_MAX_PARTS)
         return PRB_E_SIZE;
     if (((uintptr_t)qa) % 16 != 0 || ((uintptr_t)cache) % 16 != 0) return PRB_E_ALIGN;
+    if ((out == nullptr) == (out_bf == nullptr)) return PRB_E_ARG;
     LmArgs a{(const __nv_bfloat16*)qa, (const __nv_bfloat16*)cache, block_table, seq_of_token,
-             positions, item_row0, item_tokens, item_count, out, sinks, ws_o, ws_ml, ws_rows, n_items,
+             positions, item_row0, item_tokens, item_count, out, (__nv_bfloat16*)out_bf, gate, gate_ld,
+             sinks, ws_o, ws_ml, ws_rows, n_items,
              heads, rank,
              rot_dim, page_size, max_pages, num_pages, window, split_keys, splits, kw, scale,
              status};
@@ -470,8 +505,8 @@ PRB_API int prb_latent_attention_mma(float* out, const void* qa, const void* cac
     PRB_LAUNCH_CHECK();
     if (splits == 1) return 0;                 // every row had one range and is finished
     latent_merge_kernel<<<(n_items * ws_rows + 3) / 4, 128, 0, stream>>>(
-        out, ws_o, ws_ml, item_row0, item_tokens, item_count, seq_of_token, positions, sinks,
-        n_items, heads, rank, splits, split_keys, ws_rows);
+        out, (__nv_bfloat16*)out_bf, gate, gate_ld, ws_o, ws_ml, item_row0, item_tokens, item_count,
+        seq_of_token, positions, sinks, n_items, heads, rank, splits, split_keys, ws_rows);
     PRB_LAUNCH_CHECK();
     return 0;
 }

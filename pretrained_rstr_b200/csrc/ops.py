@@ -139,8 +139,10 @@ def _declare(h: ctypes.CDLL) -> None:
     h.prb_latent_prepare.argtypes = [P, L, P, P, L, I, I, P, P, P, P, P, I, I, I, I, I, I, I, F,
                                      I, I, P, P]
     h.prb_latent_fold.argtypes = [P, P, L, P, P, P, I, I, I, I, I, I, I, I, P]
-    h.prb_latent_attention_mma.argtypes = [P, P, P, P, P, P, P, P, P, I, P, P, P, I, I, I, I, I, I,
-                                           F, I, I, I, I, I, P, P]
+    h.prb_latent_attention_mma.argtypes = [P, P, P, L, P, P, P, P, P, P, P, P, I, P, P, P, I, I, I,
+                                           I, I, I, F, I, I, I, I, I, P, P]
+    h.prb_latent_rotate.argtypes = [P, P, L, P, P, I, I, I, I, I, I, P]
+    h.prb_latent_rotate.restype = c_int
     h.prb_latent_mma_supports.argtypes = [I, I, I]
     h.prb_latent_mma_single_kw.argtypes = [I]
     h.prb_latent_mma_rows.argtypes = []
@@ -1037,10 +1039,26 @@ def latent_mma_rows() -> int:
     return int(lib().prb_latent_mma_rows())
 
 
+def latent_rotate(qa, q, positions, freq, heads: int, rank: int, rot_dim: int, rot_dims: int) -> None:
+    """qa[t, h, :] = q[t, h, :] with the last ``rot_dim`` numbers of every head rotated by the
+    token's position (the first ``rot_dims`` of them, rotate-half layout).  q float32
+    [T, >= heads * (rank + rot_dim)]; qa [T, heads, rank + rot_dim], float32 or bfloat16."""
+    what = "latent_rotate"
+    d = rank + rot_dim
+    if q.dtype != torch.float32 or q.stride(1) != 1 or q.shape[1] < heads * d:
+        raise KernelArgumentError(f"{what}: q must be float32 [T, heads * (rank + rot_dim)]")
+    _need(qa, None, "qa", what)
+    if tuple(qa.shape) != (q.shape[0], heads, d):
+        raise KernelArgumentError(f"{what}: shapes do not fit")
+    _check(lib().prb_latent_rotate(_p(qa), _p(q), q.stride(0), _p(positions), _p(freq), q.shape[0],
+                                   heads, rank, rot_dim, rot_dims, dtype_code(qa.dtype), _stream()),
+           what)
+
+
 def latent_attention_mma(out, qa, cache, block_table, seq_of_token, positions, item_row0,
                          item_tokens, item_count, n_items: int, sinks, ws_o, ws_ml, scale: float,
                          window, rank: int, split_keys: int, splits: int, kw: int, ws_rows: int,
-                         status) -> None:
+                         status, gate=None) -> None:
     """The same as ``latent_attention`` on tensor cores for bfloat16 queries and cache.  Work
     items: item i is ``item_tokens[i]`` (1 if None) consecutive tokens of one request from
     token row ``item_row0[i]`` on, all heads (heads * tokens <= ``ws_rows`` <= 128); ``n_items``
@@ -1049,9 +1067,19 @@ def latent_attention_mma(out, qa, cache, block_table, seq_of_token, positions, i
     block of 64 keys ``kw`` ways (1: prompt portions, items of up to 128 rows; 4 or 2: single
     tokens of up to 16 or 32 heads).  ``ws_o`` float32 [n_items * ws_rows * splits * rank] and
     ``ws_ml`` (the same without rank, times 2) hold the partial results of the key ranges,
-    which a second kernel joins into ``out``."""
+    which a second kernel joins into ``out``.  ``out`` is float32 [T, heads, rank], or
+    bfloat16 of that shape, and then every head's rows are multiplied by sigmoid(gate[t, h])
+    when ``gate`` (float32 [T, heads], may be a column slice) is given."""
     what = "latent_attention_mma"
-    _need(out, torch.float32, "out", what)
+    _need(out, None, "out", what)
+    if out.dtype not in (torch.float32, torch.bfloat16) or (gate is not None and out.dtype != torch.bfloat16):
+        raise KernelArgumentError(f"{what}: out is float32, or bfloat16 (which may take a gate)")
+    gate_ld = 0
+    if gate is not None:
+        if gate.dtype != torch.float32 or gate.stride(1) != 1 or gate.shape[1] != qa.shape[1] or \
+                gate.shape[0] < qa.shape[0]:
+            raise KernelArgumentError(f"{what}: gate must be float32 [T, heads]")
+        gate_ld = gate.stride(0)
     _need(qa, torch.bfloat16, "qa", what)
     _need(cache, torch.bfloat16, "cache", what)
     num_pages, kv_heads, page_size, row = cache.shape
@@ -1071,7 +1099,8 @@ def latent_attention_mma(out, qa, cache, block_table, seq_of_token, positions, i
     if sinks is not None:
         _need(sinks, torch.float32, "sinks", what)
     code = lib().prb_latent_attention_mma(
-        _p(out), _p(qa), _p(cache), _p(block_table), _p(seq_of_token), _p(positions), _p(item_row0),
+        _p(out) if out.dtype == torch.float32 else None,
+        _p(out) if out.dtype == torch.bfloat16 else None, _p(gate), gate_ld, _p(qa), _p(cache), _p(block_table), _p(seq_of_token), _p(positions), _p(item_row0),
         _p(item_tokens), _p(item_count), int(n_items), _p(sinks), _p(ws_o), _p(ws_ml), heads, rank,
         d - rank, page_size, block_table.shape[1], num_pages, float(scale), int(window or 0),
         int(split_keys), int(splits), int(kw), int(ws_rows), _p(status), _stream())

@@ -15,6 +15,14 @@ key for all heads, which is what the cache holds (a group with one pool per laye
 "head").  Sizes, the rotation's base and reach, the scale, the sink and the gate are
 parameters.
 
+Two ways through a step.  float32 (and bfloat16 sizes the tensor-core kernel does not take):
+Uq, then per head the fold through Uk with the rotation, the 32-bit attention kernel, the
+unfold through Uv with the gate, the output projection.  bfloat16 on tensor cores: Uk is
+folded into Uq and Uv into the output projection when the model is built (in 32-bit, rounded
+once), so a step is the folded query product, the rotation, the attention kernel, which
+leaves the gated sums in bfloat16, and the folded output product: two kernels fewer, and
+the per-head matrices run at the products' speed.
+
 The first matrix product carries Dq, Dkv and G in one, and whatever rows an arrangement
 asks to ride along (:meth:`fuse_input_rows`); its float32 result feeds the norms unrounded.
 """
@@ -185,23 +193,43 @@ class LatentAttention(Mixer):
             self.input.add("gate", need("gate", (self.heads, self.width)))
         self.q_norm = need("q_norm", (self.q_rank,)).to(torch.float32).contiguous()
         self.kv_norm = need("kv_norm", (self.rank,)).to(torch.float32).contiguous()
-        self.q_up = padded_linear(need("q_up", (self.heads * hd, self.q_rank)), runtime)
-        self.uk = need("k_up", (self.heads * self.dim, self.rank)).to(dtype).contiguous()
-        # the value expansion with the latent axis outermost: a thread per value coordinate
-        # then reads neighbouring numbers
-        self.uvt = need("v_up", (self.heads * self.vdim, self.rank)).to(dtype) \
-            .reshape(self.heads, self.vdim, self.rank).transpose(1, 2).contiguous()
         self.sinks = need("sink", (self.heads,)).to(torch.float32).contiguous() \
             if p.get("sink", False) else None
-        self.out = padded_linear(need("out", (self.width, self.heads * self.vdim)), runtime)
-        half = self.rot_dims // 2
-        base = float(p.get("rot_base", 10000.0))
-        self.freq = torch.tensor([base ** (-2.0 * i / self.rot_dims) for i in range(half)] or [0.0],
-                                 dtype=torch.float64).to(torch.float32).to(dev)
         # bfloat16 serving: the tensor-core kernel where it takes the sizes, else (and in
         # float32) the 32-bit-arithmetic kernel
         self.tensor_cores = dtype == torch.bfloat16 and torch.cuda.is_available() and \
             ops.latent_mma_supports(self.heads, self.rank, self.rot_dim)
+        q_up = need("q_up", (self.heads * hd, self.q_rank))
+        k_up = need("k_up", (self.heads * self.dim, self.rank))
+        v_up = need("v_up", (self.heads * self.vdim, self.rank))
+        out = need("out", (self.width, self.heads * self.vdim))
+        if self.tensor_cores:
+            # Uk and Uv are folded into their neighbours once, in 32-bit: the query comes out
+            # of ONE product as [Uk_h^T q_plain | q_rot] per head, and the output projection
+            # takes the heads' gated latent sums as they leave the attention kernel
+            uq = q_up.to(torch.float32).reshape(self.heads, hd, self.q_rank)
+            uk = k_up.to(torch.float32).reshape(self.heads, self.dim, self.rank)
+            folded = torch.einsum("hdr,hdq->hrq", uk, uq[:, :self.dim])
+            self.q_fold = padded_linear(
+                torch.cat([folded, uq[:, self.dim:]], dim=1).reshape(
+                    self.heads * (self.rank + self.rot_dim), self.q_rank), runtime)
+            uv = v_up.to(torch.float32).reshape(self.heads, self.vdim, self.rank)
+            wo = out.to(torch.float32).reshape(self.width, self.heads, self.vdim)
+            self.out_fold = padded_linear(
+                torch.einsum("whv,hvr->whr", wo, uv).reshape(self.width, self.heads * self.rank),
+                runtime)
+        else:
+            self.q_up = padded_linear(q_up, runtime)
+            self.uk = k_up.to(dtype).contiguous()
+            # the value expansion with the latent axis outermost: a thread per value
+            # coordinate then reads neighbouring numbers
+            self.uvt = v_up.to(dtype).reshape(self.heads, self.vdim, self.rank) \
+                .transpose(1, 2).contiguous()
+            self.out = padded_linear(out, runtime)
+        half = self.rot_dims // 2
+        base = float(p.get("rot_base", 10000.0))
+        self.freq = torch.tensor([base ** (-2.0 * i / self.rot_dims) for i in range(half)] or [0.0],
+                                 dtype=torch.float64).to(torch.float32).to(dev)
         self.work_plan = LatentWork()
         self.tile_tokens = self.work_plan.note_mixer(self.heads)
         self.sm_count = ops.sm_count() if torch.cuda.is_available() else 148
@@ -228,24 +256,31 @@ class LatentAttention(Mixer):
         group = ctx.groups[cache.group]
         proj = self._proj = self.input.run(ctx, h)
         cols = self.input.cols
-        cq = ctx.scratch_zero("latent_cq", (cap, self.q_up.n_in), dtype)[:t]
+        first = self.q_fold if self.tensor_cores else self.q_up
+        cq = ctx.scratch_zero("latent_cq", (cap, first.n_in), dtype)[:t]
         ops.latent_prepare(cq, cache.k, proj, cols["q"][0], cols["kv"][0], self.q_norm,
                            self.kv_norm, group.slots if cache.writes else None, ctx.positions,
                            self.freq, self.q_rank, self.rank, self.rot_dim, self.rot_dims,
                            self.eps, ctx.status)
-        q = ctx.scratch("latent_q", (cap, self.q_up.n_out), torch.float32)[:t]
-        self.q_up.forward(ctx, cq, q)
-        qa = ctx.scratch("latent_qa", (cap, self.heads, self.rank + self.rot_dim),
-                         dtype if self.tensor_cores else torch.float32)[:t]
+        q = ctx.scratch("latent_q", (cap, first.n_out), torch.float32)[:t]
+        first.forward(ctx, cq, q)
+        gate = self.input.view(proj, "gate") if self.head_gate else None
+        width = self.rank + self.rot_dim
+        if self.tensor_cores:
+            qa = ctx.scratch("latent_qa", (cap, self.heads, width), dtype)[:t]
+            ops.latent_rotate(qa, q, ctx.positions, self.freq, self.heads, self.rank, self.rot_dim,
+                              self.rot_dims)
+            gated = ctx.scratch("latent_gated", (cap, self.heads, self.rank), dtype)[:t]
+            self._attend_tensor_cores(ctx, gated, qa, cache, group, gate)
+            self.out_fold.forward(ctx, gated.view(t, self.heads * self.rank), x,
+                                  resid=x if accumulate else None)
+            return
+        qa = ctx.scratch("latent_qa", (cap, self.heads, width), torch.float32)[:t]
         ops.latent_fold(qa, q, self.uk, ctx.positions, self.freq, self.heads, self.dim,
                         self.rot_dim, self.rot_dims, self.rank)
         lat = ctx.scratch("latent_sum", (cap, self.heads, self.rank), torch.float32)[:t]
-        if self.tensor_cores:
-            self._attend_tensor_cores(ctx, lat, qa, cache, group)
-        else:
-            attend_latent(ctx, lat, qa, cache, group, self.sinks, self.scale, self.window, self.rank)
+        attend_latent(ctx, lat, qa, cache, group, self.sinks, self.scale, self.window, self.rank)
         o = ctx.scratch_zero("latent_o", (cap, self.out.n_in), dtype)[:t]
-        gate = self.input.view(proj, "gate") if self.head_gate else None
         ops.latent_unfold(o, lat, self.uvt, gate, self.heads, self.rank, self.vdim)
         self.out.forward(ctx, o, x, resid=x if accumulate else None)
 
@@ -253,7 +288,7 @@ class LatentAttention(Mixer):
     #: most key ranges of a launch: single tokens, prompt tiles
     MAX_SPLITS = (32, 8)
 
-    def _attend_tensor_cores(self, ctx, lat, qa, cache: LayerCache, group) -> None:
+    def _attend_tensor_cores(self, ctx, lat, qa, cache: LayerCache, group, gate=None) -> None:
         """Single tokens and prompt tiles as two launches (each only if the step has such
         work; a step that is replayed from a graph launches a list's capacity and lets the
         device-side count bound it)."""
@@ -278,7 +313,7 @@ class LatentAttention(Mixer):
                 lat, qa, cache.k, group.block_table, ctx.seq_of_token, ctx.positions,
                 work.arrays[rows_name], work.arrays[tokens_name] if tokens_name else None,
                 work.counts[counter], n, self.sinks, ws_o, ws_ml, self.scale, self.window,
-                self.rank, split_keys, splits, kw, ws_rows, ctx.status)
+                self.rank, split_keys, splits, kw, ws_rows, ctx.status, gate=gate)
 
 
 def attend_latent(ctx, lat, qa, cache: LayerCache, group, sinks, scale: float,

@@ -487,6 +487,24 @@ def test_latent_mixer_chain(dtype):
     assert torch.allclose(got, want, atol=tol, rtol=tol), float((got - want).abs().max())
 
 
+def test_rotate_kernel():
+    """The rotation alone: the last rot_dim numbers of every head, the first rot_dims of
+    them in the rotate-half layout, the rest and the head's first part untouched."""
+    from pretrained_rstr_b200.csrc import ops
+    heads, rank, rot_dim, rot_dims, t = 3, 16, 12, 8, 9
+    g = torch.Generator().manual_seed(15)
+    q = torch.randn(t, heads * (rank + rot_dim) + 4, generator=g)
+    pos = torch.tensor([0, 1, 5, 63, 64, 200, 1000, 4095, 77], dtype=torch.int32)
+    freq = torch.tensor([31.0 ** (-2.0 * i / rot_dims) for i in range(rot_dims // 2)])
+    for dtype, tol in ((torch.float32, 2e-4), (torch.bfloat16, 2e-2)):
+        qa = torch.empty(t, heads, rank + rot_dim, dtype=dtype, device=DEV)
+        ops.latent_rotate(qa, q.to(DEV), pos.to(DEV), freq.to(DEV), heads, rank, rot_dim, rot_dims)
+        src = q[:, :heads * (rank + rot_dim)].reshape(t, heads, rank + rot_dim).double()
+        want = src.clone()
+        want[..., rank:] = P.rotate(src[..., rank:], pos, 31.0, rot_dims)
+        assert torch.allclose(qa.cpu().double(), want, atol=tol, rtol=tol)
+
+
 # ------------------------------------------------------- whole models through the step function
 @pytest.mark.parametrize("name,dtype", CASES)
 def test_whole_decode_portions(folders, name, dtype):
