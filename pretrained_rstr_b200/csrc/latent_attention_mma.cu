@@ -143,12 +143,17 @@ latent_mma_kernel(LmArgs a) {
     // copies that do not wait for one another
     constexpr int TPR = LM_THREADS / LM_KEYS;              // threads per key row
     const int lrow = tid / TPR, lsub = tid - lrow * TPR;
-    auto load_keys = [&](int kb, __nv_bfloat16* dst) {
+    // (the page of a block's row is asked for a block ahead of its copies, so that the copies
+    // do not wait for the block table)
+    auto page_of = [&](int kb) {
+        const int j = kb + lrow;
+        return j < k_end ? table[j / a.page_size] : -1;
+    };
+    auto load_keys = [&](int kb, __nv_bfloat16* dst, int page) {
         const int j = kb + lrow;
         bool ok = j < k_end;
         const __nv_bfloat16* src = a.cache;
         if (ok) {
-            const int page = table[j / a.page_size];
             if (page < 0 || page >= a.num_pages) {
                 if (lsub == 0 && j >= lo_min) prb_set_status(a.status, PRB_S_PAGE_RANGE, t0, j, page);
                 ok = false;
@@ -159,8 +164,9 @@ latent_mma_kernel(LmArgs a) {
         for (int k = lsub; k < chunks; k += TPR)
             cp_async16(dst + lrow * LD + k * 8, ok ? src + k * 8 : src, ok);
     };
-    load_keys(kb_first, kbuf[0]);
+    load_keys(kb_first, kbuf[0], page_of(kb_first));
     cp_async_commit();
+    int page_next = page_of(kb_first + LM_KEYS);
 
     const int kw = a.kw, mt = warp / kw, kq = warp - mt * kw;
     const int kpw = LM_KEYS / kw, nts = kpw / 8;           // keys and score tiles of this warp a block
@@ -177,8 +183,9 @@ latent_mma_kernel(LmArgs a) {
 
     int buf = 0;
     for (int kb = kb_first; kb < k_end; kb += LM_KEYS, buf ^= 1) {
-        if (kb + LM_KEYS < k_end) load_keys(kb + LM_KEYS, kbuf[buf ^ 1]);
+        if (kb + LM_KEYS < k_end) load_keys(kb + LM_KEYS, kbuf[buf ^ 1], page_next);
         cp_async_commit();
+        page_next = page_of(kb + 2 * LM_KEYS);
         cp_async_wait<1>();
         __syncthreads();
         const __nv_bfloat16* ks = kbuf[buf];
@@ -186,6 +193,7 @@ latent_mma_kernel(LmArgs a) {
             float s[8][4];
 #pragma unroll
             for (int i = 0; i < 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.0f;
+#pragma unroll 2
             for (int kk = 0; kk < D / 16; ++kk) {
                 uint32_t qa[4];
                 ldsm_x4(qa, qs + (mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LD + kk * 16 +
@@ -421,22 +429,32 @@ latent_merge_kernel(float* __restrict__ out, __nv_bfloat16* __restrict__ out_bf,
     const float denom = prb_warp_sum(l * f) + (sinks ? expf(sk - top) : 0.0f);
     float inv = denom > 0.0f ? 1.0f / denom : 0.0f;
     if (ob) inv *= lm_gate(gate, gate_ld, t, h);
-    for (int d0 = 0; d0 < rank; d0 += 32) {
-        const int d = d0 + lane;
-        float acc = 0.0f;
-        for (int p0 = 0; p0 < n; p0 += 8) {               // eight parts' loads in flight at once
-            float v[8];
+    float acc[8];                                          // (rank <= 256: eight per lane)
 #pragma unroll
-            for (int i = 0; i < 8; ++i)
-                v[i] = (p0 + i < n && d < rank) ? ws_o[(base + p0 + i) * rank + d] : 0.0f;
+    for (int k = 0; k < 8; ++k) acc[k] = 0.0f;
+    for (int p0 = 0; p0 < n; p0 += 4) {                    // four parts' rows in flight at once
+        float v[4][8];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const float fp = __shfl_sync(0xffffffffu, f, (p0 + i) & 31);
-                if (p0 + i < n && fp != 0.0f) acc = fmaf(v[i], fp, acc);
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const int d = lane + 32 * k;
+                v[i][k] = (p0 + i < n && d < rank) ? ws_o[(base + p0 + i) * rank + d] : 0.0f;
+            }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float fp = __shfl_sync(0xffffffffu, f, (p0 + i) & 31);
+            if (p0 + i < n && fp != 0.0f) {
+#pragma unroll
+                for (int k = 0; k < 8; ++k) acc[k] = fmaf(v[i][k], fp, acc[k]);
             }
         }
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        const int d = lane + 32 * k;
         if (d < rank) {
-            if (ob) ob[d] = __float2bfloat16_rn(acc * inv); else o[d] = acc * inv;
+            if (ob) ob[d] = __float2bfloat16_rn(acc[k] * inv); else o[d] = acc[k] * inv;
         }
     }
 }
