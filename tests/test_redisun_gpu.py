@@ -620,3 +620,40 @@ def test_greedy_generation_entry_point(folders, dtype):
     cache = m.engine.lm.cache
     assert not cache.requests and cache.free_pages(0) == cache.allocators[0].num_pages
     cache.check()
+
+
+def test_replay_and_generate_as_programs(folders, tmp_path):
+    """``bin/trace_run`` and ``python -m pretrained_rstr_b200 generate`` on a Redisun folder:
+    the model class comes from config.json; logits of a replayed trace match the plain ones."""
+    import json
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    folder = folders[("A", "float32")]
+    cfg, tensors = P.read_folder(folder)
+    ids = random_tokens(40, cfg["vocab"], 77)
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": ids[:30], "want": [0, 29]}], "end": []},
+             {"step": 1, "entries": [{"id": "a", "tokens": ids[30:32], "want": []},
+                                     {"id": "b", "tokens": ids[:3], "want": [2]}], "end": ["b"]},
+             {"step": 2, "entries": [{"id": "a", "tokens": ids[32:], "want": [7]}], "end": ["a"]}]
+    out = tmp_path / "out"
+    proc = subprocess.run([os.path.join(root, "bin", "trace_run"), "--model", folder, "--dtype",
+                           "float32", "--out", str(out), "--max-tokens", "128"],
+                          input="\n".join(json.dumps(s) for s in steps) + "\n", text=True,
+                          capture_output=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert [l for l in proc.stdout.splitlines() if l.startswith("done")] == ["done 0", "done 1", "done 2"]
+    want = P.forward(ids, tensors, cfg).to(torch.float32)
+    import numpy as np
+    got0 = torch.from_numpy(np.fromfile(out / "0.f32", dtype="<f4").reshape(2, -1))
+    got1 = torch.from_numpy(np.fromfile(out / "1.f32", dtype="<f4").reshape(1, -1))
+    got2 = torch.from_numpy(np.fromfile(out / "2.f32", dtype="<f4").reshape(1, -1))
+    for row, pos in ((got0[0], 0), (got0[1], 29), (got1[0], 2), (got2[0], 39)):
+        assert row_error(row, want[pos]) < TOL["float32"]
+    proc = subprocess.run([sys.executable, "-m", "pretrained_rstr_b200", "generate", "--model", folder,
+                           "--dtype", "float32", "--ids", ",".join(map(str, ids[:9])), "--n", "5",
+                           "--maxpos", "64"], cwd=root, capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    rec = json.loads(proc.stdout.strip().splitlines()[-1])
+    assert rec["generated"] == P.greedy(ids[:9], 5, tensors, cfg)
