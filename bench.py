@@ -149,6 +149,8 @@ def main() -> int:
                     help="the host's side of a decode step: wall time a step with a one-layer model, cProfile shares")
     ap.add_argument("--profile-decode-attention", default=None, metavar="HEADS,REQUESTS,CONTEXT",
                     help="the decode attention kernel alone, by split size")
+    ap.add_argument("--profile-latent", default=None, metavar="HEADS,RANK,ROT,ITEMS,CONTEXT[,TOKENS]",
+                    help="the tensor-core attention over shared latent rows alone, by key range")
     ap.add_argument("--profile-sample", default=None, metavar="ROWS,VOCAB,K",
                     help="the sampling kernel alone")
     ap.add_argument("--kernel-table", action="store_true",
@@ -197,6 +199,8 @@ def main() -> int:
         return profiles.profile_decode_attention(args.profile_decode_attention)
     if args.profile_sample:
         return profiles.profile_sample(args.profile_sample)
+    if args.profile_latent:
+        return profiles.profile_latent_attention(args.profile_latent)
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2

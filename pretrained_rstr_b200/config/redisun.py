@@ -168,9 +168,12 @@ class RedisunConfig(ModelConfig):
             gates = {"mixer": p + "rg1"}
             if mlp is not None:
                 gates["feed_forward"] = p + "rg2"
+            params = {"alpha": self.postln_alpha, "gates": gates}
+            if mlp is None:
+                params["norm_alone"] = {"gain": p + "norm2", "eps": self.eps}
             specs.append(LayerSpec(prefix=p, arrangement="post_norm_gated", mixer=mixer,
                                    feed_forward=ff, norms=norms, width=self.width,
-                                   arrangement_params={"alpha": self.postln_alpha, "gates": gates}))
+                                   arrangement_params=params))
         return specs
 
     def embedding_spec(self) -> PartSpec:

@@ -472,3 +472,66 @@ def profile_sample(spec: str) -> int:
 
     print(json.dumps({"profile_sample": spec, "mbytes": round(rows * vocab * 4 / 1e6, 2), **res}))
     return 0
+
+
+def profile_latent_attention(spec: str) -> int:
+    """The tensor-core attention over shared latent rows alone.  ``spec`` is
+    "HEADS,RANK,ROT,ITEMS,CONTEXT[,TOKENS]": ITEMS work items of TOKENS consecutive tokens each
+    (1: decoded tokens, the warps split the keys; more: prompt tiles) at CONTEXT cached tokens;
+    device microseconds by size of the key ranges, with the rates the bytes and operations give."""
+    import torch
+    from ..csrc import ops
+    from .roofline import peaks
+    parts = [int(x) for x in spec.split(",")]
+    heads, rank, rot, n_items, ctx = parts[:5]
+    tq = parts[5] if len(parts) > 5 else 1
+    dev, d, page = "cuda:0", rank + rot, 64
+    pages_per = -(-ctx // page)
+    cache = (torch.randn(n_items * pages_per + 1, 1, page, d, device=dev) * 0.3).to(torch.bfloat16)
+    table = torch.arange(n_items * pages_per, dtype=torch.int32, device=dev).reshape(n_items, pages_per)
+    t = n_items * tq
+    qa = torch.randn(t, heads, d, device=dev).to(torch.bfloat16)
+    seq = torch.arange(n_items, dtype=torch.int32, device=dev).repeat_interleave(tq)
+    pos = (torch.arange(tq, dtype=torch.int32, device=dev) + (ctx - tq)).repeat(n_items)
+    row0 = torch.arange(0, t, tq, dtype=torch.int32, device=dev)
+    single = tq == 1
+    toks = None if single else torch.full((n_items,), tq, dtype=torch.int32, device=dev)
+    kw = ops.latent_mma_single_kw(heads) if single else 1
+    ws_rows = heads if single else ops.latent_mma_rows()
+    out = torch.empty(t, heads, rank, device=dev, dtype=torch.bfloat16)
+    status = torch.zeros(4, dtype=torch.int32, device=dev)
+    flush = torch.empty(160 << 20, dtype=torch.uint8, device=dev)
+    pk = peaks()
+    results = {}
+    for split_keys in sorted({64, 128, 256, -(-ctx // 64) * 64}):
+        splits = -(-ctx // split_keys)
+        if splits > 32:
+            continue
+        ws_o = torch.empty(n_items * ws_rows * splits * rank, device=dev)
+        ws_ml = torch.empty(n_items * ws_rows * splits * 2, device=dev)
+
+        def run():
+            ops.latent_attention_mma(out, qa, cache, table, seq, pos, row0, toks, None, n_items,
+                                     None, ws_o, ws_ml, 0.1, None, rank, split_keys, splits, kw,
+                                     ws_rows, status)
+        for _ in range(3):
+            run()
+        times = []
+        for _ in range(10):
+            flush.zero_()                                   # (the cache rows come from memory)
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            run()
+            e.record()
+            torch.cuda.synchronize()
+            times.append(s.elapsed_time(e) * 1e3)
+        us = sorted(times)[len(times) // 2]
+        nbytes = n_items * ctx * d * 2 + t * heads * (d + rank) * 2
+        flops = 2.0 * t * heads * (ctx - (tq - 1) / 2.0) * (d + rank)
+        results[split_keys] = {"us": round(us, 2), "gb_s": round(nbytes / us / 1e3, 1),
+                               "tflop_s": round(flops / us / 1e6, 2),
+                               "hbm_frac": round(nbytes / us / 1e3 / pk["hbm_gbs"], 4),
+                               "bf16_frac": round(flops / us / 1e6 / pk["bf16_tflops"], 4)}
+    assert int(status[0]) == 0
+    print(json.dumps({"profile_latent_attention": spec, "by_split_keys": results}))
+    return 0

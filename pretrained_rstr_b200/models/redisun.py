@@ -54,6 +54,9 @@ def expected_tensors(cfg: RedisunConfig) -> Dict[str, TensorExpectation]:
             p + "mix.o": TensorExpectation((d, h * vd)),
         })
         if mlp is None:
+            # (a file may still carry the second norm of a layer without a feed-forward; it is
+            # then applied to the scaled stream alone)
+            exp[p + "norm2"] = TensorExpectation((), optional=True)
             continue
         exp.update({p + "norm2": TensorExpectation(()),
                     p + "rg2": TensorExpectation((d, d)), p + "rg2.b": TensorExpectation((d,))})
@@ -75,6 +78,8 @@ def random_tensors(cfg: RedisunConfig, seed: int) -> Dict[str, torch.Tensor]:
     1 + N(0, 0.1), sinks and biases N(0, 0.5); every tensor from a generator of its own."""
     out: Dict[str, torch.Tensor] = {}
     for name, exp in expected_tensors(cfg).items():
+        if exp.optional:
+            continue
         if name in ("embed", "bigram"):
             out[name] = normal(seed, name, exp.shape, 1.0)
         elif name.endswith(("norm", "norm1", "norm2")):
@@ -110,8 +115,9 @@ def _sized(vocab, width, layers, buckets):
 #: Sizes a random-weight model can be asked for by name.  ``redisun-small`` has the width,
 #: depth, head count and vocabulary of GPT-2 small (its gated feed-forward of 2,048 holds as
 #: many numbers as GPT-2's of 3,072); ``redisun-small-moe`` swaps every second feed-forward
-#: for eight experts of which two run, plus a shared one; ``redisun-wide`` is a wider latent
-#: (rank 512, 64 rotated dimensions) at GPT-2 XL's width.
+#: for eight experts of which two run, plus a shared one; ``redisun-wide`` has GPT-2 XL's width
+#: and head count with heads of 128 + 64 dimensions over a latent of 256 (the most the
+#: tensor-core attention kernel takes; a wider latent runs on the 32-bit-arithmetic kernel).
 NAMED_SIZES = {
     "redisun-tiny": _sized(384, 48, [
         _layer(3, 16, 8, 16, 24, 16, {"kind": "dense", "ff": 64}),
@@ -124,7 +130,7 @@ NAMED_SIZES = {
                {"kind": "dense", "ff": 2048} if i % 2 == 0 else _moe(8, 2, 512, 1024))
         for i in range(12)], 65521),
     "redisun-wide": _sized(50257, 1600, [
-        _layer(25, 128, 64, 128, 512, 768, {"kind": "dense", "ff": 4096}) for _ in range(12)], 65521),
+        _layer(25, 128, 64, 128, 256, 768, {"kind": "dense", "ff": 4096}) for _ in range(12)], 65521),
 }
 
 

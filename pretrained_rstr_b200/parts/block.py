@@ -45,7 +45,9 @@ class PostNormGatedBlock(Block):
     """x <- norm_1(alpha x + g_1(x) * mixer(x)); x <- norm_2(alpha x + g_2(x) * feed_forward(x)):
     the branches read the stream itself, the norm comes after the sum, and a branch's result may
     be gated element by element by g(x) = sigmoid(W x + b) (``params["gates"]``: branch name ->
-    tensor name of W, with ``.b``).  A layer without a feed-forward has the first half only.
+    tensor name of W, with ``.b``).  A layer without a feed-forward has the first half only
+    (and, if its file still holds a second norm, ``params["norm_alone"]``, that norm of the
+    scaled stream).
 
     The gate's matrix rides along in the branch's first matrix product where the part offers
     that (``fuse_input_rows``); sum, gate and norm are one kernel, which also leaves the
@@ -70,6 +72,13 @@ class PostNormGatedBlock(Block):
         for norm in norms.values():
             if not hasattr(norm, "joined"):
                 raise ValueError("post_norm_gated needs norms that can join a branch to the stream")
+        # a layer without a feed-forward whose file still holds the second norm: x <- norm(alpha x)
+        self.norm_alone = None
+        alone = params.get("norm_alone")
+        if not self.has_ff and alone and store is not None and alone["gain"] in store:
+            from .norms import RMSNorm
+            self.norm_alone = RMSNorm(store.get(alone["gain"]), None, alone["eps"], width)
+            self.norms["alone"] = self.norm_alone
         self.gates = {}
         for name, tensor in (params.get("gates") or {}).items():
             part = {"mixer": mixer, "feed_forward": feed_forward}[name]
@@ -114,6 +123,8 @@ class PostNormGatedBlock(Block):
                     own.forward(ctx, h, gate)
             self.norms[name].joined(ctx, x, y, self.alpha, gate=gate, gate_bias=bias, copy=copy)
             current = True
+        if self.norm_alone is not None:
+            self.norm_alone.joined(ctx, x, None, self.alpha, copy=copy)
         ctx.stream_copy_by = self
 
 

@@ -171,6 +171,8 @@ def layer(x: torch.Tensor, tensors, i: int, spec: dict, cfg: dict,
             gaps.append(router_gap(x, tensors, p + "mlp.", spec["mlp"]))
         y = feed_forward(x, tensors, p, spec["mlp"]) * residual_gate(x, tensors, p + "rg2")
         x = scalar_norm(alpha * x + y, tensors[p + "norm2"].to(x.dtype), eps)
+    elif p + "norm2" in tensors:               # no feed-forward, yet a second norm in the file
+        x = scalar_norm(alpha * x, tensors[p + "norm2"].to(x.dtype), eps)
     return x
 
 

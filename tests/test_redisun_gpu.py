@@ -657,3 +657,25 @@ def test_replay_and_generate_as_programs(folders, tmp_path):
     assert proc.returncode == 0, proc.stderr[-2000:]
     rec = json.loads(proc.stdout.strip().splitlines()[-1])
     assert rec["generated"] == P.greedy(ids[:9], 5, tensors, cfg)
+
+
+def test_second_norm_without_a_feed_forward(folders, tmp_path):
+    """A file that holds the second norm of a layer without a feed-forward: the norm is
+    applied to the scaled stream alone."""
+    import shutil
+    from pretrained_rstr_b200.weights.safetensors_io import save_file
+    src = folders[("A", "float32")]
+    cfg, tensors = P.read_folder(src)
+    assert cfg["layers"][2]["mlp"] is None and "l2.norm2" not in tensors
+    tensors["l2.norm2"] = torch.tensor(1.3)
+    folder = str(tmp_path / "with_norm2")
+    shutil.copytree(src, folder)
+    save_file(tensors, folder + "/model.safetensors")
+    prompts = {"r0": random_tokens(70, cfg["vocab"], 5)}
+    oracle = _oracle(folder, prompts)
+    rp = Replayer(folder, "float32", max_tokens=128)
+    rp.step([("r0", prompts["r0"][:40], list(range(40)))])
+    rp.step([("r0", prompts["r0"][40:], list(range(30)))], end=["r0"])
+    compare(rp.rows, oracle, TOL["float32"])
+    plain_without = P.forward(prompts["r0"], P.read_folder(src)[1], cfg).to(torch.float32)
+    assert row_error(oracle["r0"][69], plain_without[69]) > 1e-3        # the norm matters
