@@ -26,6 +26,7 @@ __global__ void embed_pair_kernel(float* __restrict__ out, const int* __restrict
                                   const W* __restrict__ pairs, int n_tokens, int width, int vocab,
                                   long long buckets, long long mul_prev, long long mul_cur,
                                   int n_slots, int b_cap, int* status) {
+    prb_grid_launch_dependents();          // (a product that follows may set itself up meanwhile)
     const int t = blockIdx.x;
     if (t >= n_tokens) return;
     float* o = out + (size_t)t * width;
@@ -75,6 +76,7 @@ template <typename O>
 __global__ void rms_norm_kernel(RmsArgs a) {
     extern __shared__ float row[];
     __shared__ float scratch[32];
+    prb_grid_launch_dependents();
     const int r = blockIdx.x;
     if (r >= a.n_rows) return;
     const int width = a.width;
@@ -118,6 +120,7 @@ __global__ void gated_pair_kernel(O* __restrict__ out, long out_ld, int out_col,
                                   const float* __restrict__ in, long in_ld, int gate_col, int up_col,
                                   int n, int n_rows, float limit, float act_alpha, float up_shift,
                                   const float* __restrict__ scale, long scale_ld, int group) {
+    prb_grid_launch_dependents();
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= (size_t)n_rows * n) return;
     const int t = (int)(idx / n), i = (int)(idx - (size_t)t * n);
@@ -132,6 +135,42 @@ __global__ void gated_pair_kernel(O* __restrict__ out, long out_ld, int out_col,
     out[(size_t)t * out_ld + out_col + i] = prb_from_float<O>(v);
 }
 
+// The same, four neighbouring columns a thread (16-byte loads; n, the columns' offsets, the
+// row pitches and the group all multiples of 4).
+template <typename O>
+__global__ void gated_pair4_kernel(O* __restrict__ out, long out_ld, int out_col,
+                                   const float* __restrict__ in, long in_ld, int gate_col, int up_col,
+                                   int n, int n_rows, float limit, float act_alpha, float up_shift,
+                                   const float* __restrict__ scale, long scale_ld, int group) {
+    prb_grid_launch_dependents();
+    const int n4 = n / 4;
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (size_t)n_rows * n4) return;
+    const int t = (int)(idx / n4), i = (int)(idx - (size_t)t * n4) * 4;
+    const float4 g4 = *reinterpret_cast<const float4*>(in + (size_t)t * in_ld + gate_col + i);
+    const float4 u4 = *reinterpret_cast<const float4*>(in + (size_t)t * in_ld + up_col + i);
+    const float sc = scale ? scale[(size_t)t * scale_ld + i / group] : 1.0f;
+    float g[4] = {g4.x, g4.y, g4.z, g4.w}, u[4] = {u4.x, u4.y, u4.z, u4.w}, v[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        if (limit > 0.0f) {
+            g[k] = fminf(g[k], limit);
+            u[k] = fminf(fmaxf(u[k], -limit), limit);
+        }
+        v[k] = g[k] * sigmoidf_(act_alpha * g[k]) * (u[k] + up_shift) * sc;
+    }
+    O* o = out + (size_t)t * out_ld + out_col + i;
+    if constexpr (sizeof(O) == 4) {
+        *reinterpret_cast<float4*>(o) = make_float4(v[0], v[1], v[2], v[3]);
+    } else {
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]), hi = __floats2bfloat162_rn(v[2], v[3]);
+        uint2 pk;
+        pk.x = *reinterpret_cast<const uint32_t*>(&lo);
+        pk.y = *reinterpret_cast<const uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(o) = pk;
+    }
+}
+
 // ------------------------------------------------------------------------- router
 // z[e] = x . w[e] + bias[e] in 32-bit; the `top` largest (ties: the lower index); their
 // weights are the softmax over those alone.  With w == null, x[t, :n_experts] are logits a
@@ -143,6 +182,7 @@ __global__ void route_kernel(float* __restrict__ scale, int* __restrict__ chosen
                              const W* __restrict__ w, const float* __restrict__ bias, int n_tokens,
                              int width, int n_experts, int top) {
     extern __shared__ float z[];                 // [n_experts]
+    prb_grid_launch_dependents();
     const int t = blockIdx.x;
     if (t >= n_tokens) return;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
@@ -245,6 +285,22 @@ PRB_API int prb_gated_pair(void* out, long out_ld, int out_col, const float* in,
     if (n <= 0 || n_rows <= 0) return 0;
     if (scale != nullptr && group <= 0) return PRB_E_ARG;
     const size_t total = (size_t)n * n_rows;
+    const size_t esz = out_dtype == PRB_F32 ? 4 : 2;
+    if (n % 4 == 0 && gate_col % 4 == 0 && up_col % 4 == 0 && out_col % 4 == 0 && in_ld % 4 == 0 &&
+        out_ld % 4 == 0 && (scale == nullptr || group % 4 == 0) && ((uintptr_t)in) % 16 == 0 &&
+        ((uintptr_t)out) % (4 * esz) == 0 && (out_dtype == PRB_F32 || out_dtype == PRB_BF16)) {
+        const unsigned blocks4 = (unsigned)((total / 4 + 255) / 256);
+        if (out_dtype == PRB_F32)
+            gated_pair4_kernel<float><<<blocks4, 256, 0, stream>>>(
+                (float*)out, out_ld, out_col, in, in_ld, gate_col, up_col, n, n_rows, limit,
+                act_alpha, up_shift, scale, scale_ld, group);
+        else
+            gated_pair4_kernel<__nv_bfloat16><<<blocks4, 256, 0, stream>>>(
+                (__nv_bfloat16*)out, out_ld, out_col, in, in_ld, gate_col, up_col, n, n_rows, limit,
+                act_alpha, up_shift, scale, scale_ld, group);
+        PRB_LAUNCH_CHECK();
+        return 0;
+    }
     const unsigned blocks = (unsigned)((total + 255) / 256);
     if (out_dtype == PRB_F32)
         gated_pair_kernel<float><<<blocks, 256, 0, stream>>>(

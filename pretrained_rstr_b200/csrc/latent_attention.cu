@@ -43,6 +43,7 @@ latent_prepare_kernel(A* __restrict__ cq, long cq_ld, C* __restrict__ cache,
                       int rot_dim, int rot_dims, int page_size, int num_pages, float eps,
                       int* status) {
     __shared__ float scratch[32];
+    prb_grid_launch_dependents();          // (a product that follows may set itself up meanwhile)
     const int t = blockIdx.x;
     if (t >= n_tokens) return;
     const float* p = proj + (size_t)t * ld;
@@ -164,6 +165,7 @@ __global__ void __launch_bounds__(256)
 latent_rotate_kernel(O* __restrict__ qa, const float* __restrict__ q, long ld,
                      const int* __restrict__ positions, const float* __restrict__ freq,
                      int n_tokens, int heads, int rank, int rot_dim, int rot_dims) {
+    prb_grid_launch_dependents();
     const int t = blockIdx.x;
     if (t >= n_tokens) return;
     const int D = rank + rot_dim, half = rot_dims / 2;

@@ -108,6 +108,7 @@ latent_mma_kernel(LmArgs a) {
     const int q_rows = 16 * WARPS / a.kw;                 // rows of the item's tile
     __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(lm_smem);
     __nv_bfloat16* kbuf[2] = {qs + q_rows * LD, qs + (q_rows + LM_KEYS) * LD};
+    prb_grid_launch_dependents();          // (a product that follows may set itself up meanwhile)
     const int item = blockIdx.x, split = blockIdx.y;
     if (item >= a.n_items || (a.item_count != nullptr && item >= *a.item_count)) return;
     const int t0 = a.item_row0[item];
@@ -404,6 +405,7 @@ latent_merge_kernel(float* __restrict__ out, __nv_bfloat16* __restrict__ out_bf,
                     const int* __restrict__ seq_of_token, const int* __restrict__ positions,
                     const float* __restrict__ sinks, int n_items, int heads, int rank, int parts,
                     int split_keys, int ws_rows) {
+    prb_grid_launch_dependents();
     const int unit = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     const int item = unit / ws_rows, row = unit - item * ws_rows;
     if (item >= n_items || (item_count != nullptr && item >= *item_count)) return;
