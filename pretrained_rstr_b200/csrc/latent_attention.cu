@@ -9,7 +9,6 @@
 //
 //   prb_latent_prepare   norms the two latents of a token, rotates r, writes the cache row
 //   prb_latent_fold      q -> qa: the product with Uk_h per head, the rotation of the rest
-//   prb_latent_rotate    the rotation alone, for a query whose matrix has Uk folded in
 //   prb_latent_attention scores, softmax with an optional sink per head, sum_j w_j c_j
 //   prb_latent_unfold    Uv_h (.) per head, times sigmoid(gate) per head
 //
@@ -154,36 +153,6 @@ latent_fold_kernel(O* __restrict__ qa, const float* __restrict__ q, long ld,
 #pragma unroll
         for (int sl = 1; sl < LA_SLICES; ++sl) v += part[sl][j][l];
         qa[((size_t)(t0 + j) * heads + h) * D + rr] = prb_from_float<O>(v);
-    }
-}
-
-// One CTA per token.  q: float32 [T, ld] holds heads x [rank numbers | rot_dim numbers]: a
-// query that a matrix with Uk folded into it has made; the second part of every head is
-// rotated by the token's position, and all of it goes to qa [T, heads, rank + rot_dim] in O.
-template <typename O>
-__global__ void __launch_bounds__(256)
-latent_rotate_kernel(O* __restrict__ qa, const float* __restrict__ q, long ld,
-                     const int* __restrict__ positions, const float* __restrict__ freq,
-                     int n_tokens, int heads, int rank, int rot_dim, int rot_dims) {
-    prb_grid_launch_dependents();
-    const int t = blockIdx.x;
-    if (t >= n_tokens) return;
-    const int D = rank + rot_dim, half = rot_dims / 2;
-    const float pos = (float)positions[t];
-    const float* row = q + (size_t)t * ld;
-    for (int e = threadIdx.x; e < heads * D; e += blockDim.x) {
-        const int h = e / D, i = e - h * D - rank;
-        float v = row[e];
-        if (i >= 0 && i < half) {
-            float sn, cs;
-            sincosf(pos * freq[i], &sn, &cs);
-            v = v * cs - row[e + half] * sn;
-        } else if (i >= half && i < rot_dims) {
-            float sn, cs;
-            sincosf(pos * freq[i - half], &sn, &cs);
-            v = v * cs + row[e - half] * sn;
-        }
-        qa[(size_t)t * heads * D + e] = prb_from_float<O>(v);
     }
 }
 
@@ -374,24 +343,6 @@ PRB_API int prb_latent_fold(void* qa, const float* q, long ld, const void* uk,
         latent_fold_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, LA_THREADS, smem, stream>>>(
             (__nv_bfloat16*)qa, q, ld, (const __nv_bfloat16*)uk, positions, freq, n_tokens, heads,
             dim, rot_dim, rot_dims, rank);
-    else
-        return PRB_E_DTYPE;
-    PRB_LAUNCH_CHECK();
-    return 0;
-}
-
-PRB_API int prb_latent_rotate(void* qa, const float* q, long ld, const int* positions,
-                              const float* freq, int n_tokens, int heads, int rank, int rot_dim,
-                              int rot_dims, int out_dtype, cudaStream_t stream) {
-    if (n_tokens <= 0) return 0;
-    if (heads <= 0 || rank <= 0 || rot_dim < 0 || rot_dims > rot_dim || rot_dims % 2 != 0)
-        return PRB_E_SIZE;
-    if (out_dtype == PRB_F32)
-        latent_rotate_kernel<float><<<n_tokens, 256, 0, stream>>>(
-            (float*)qa, q, ld, positions, freq, n_tokens, heads, rank, rot_dim, rot_dims);
-    else if (out_dtype == PRB_BF16)
-        latent_rotate_kernel<__nv_bfloat16><<<n_tokens, 256, 0, stream>>>(
-            (__nv_bfloat16*)qa, q, ld, positions, freq, n_tokens, heads, rank, rot_dim, rot_dims);
     else
         return PRB_E_DTYPE;
     PRB_LAUNCH_CHECK();

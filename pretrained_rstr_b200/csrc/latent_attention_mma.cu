@@ -40,6 +40,8 @@ struct LmArgs {
     const float* gate;            // [T, gate_ld], head h at column h; or null
     long gate_ld;
     const float* sinks;           // [heads] or null
+    const float* freq;            // [rot_dims / 2], or null: the queries come rotated
+    int rot_dims;                 // how many of the rot_dim numbers the rotation covers
     float* ws_o;                  // [(item * ws_rows + row) * parts + part][rank]
     float* ws_ml;                 // [(item * ws_rows + row) * parts + part][2]
     int ws_rows;                  // rows an item has room for in the workspace
@@ -189,6 +191,21 @@ latent_mma_kernel(LmArgs a) {
         page_next = page_of(kb + 2 * LM_KEYS);
         cp_async_wait<1>();
         __syncthreads();
+        if (a.freq != nullptr && kb == kb_first) {
+            // the queries arrived as their product left them: the last rot_dim numbers of a row
+            // are rotated here by the row's position (pairs i, i + rot_dims / 2; 32-bit)
+            const int half = a.rot_dims / 2;
+            for (int e = tid; e < nrows * half; e += LM_THREADS) {
+                const int r = e / half, i = e - r * half;
+                __nv_bfloat16* p = qs + r * LD + a.rank + i;
+                const float u = __bfloat162float(p[0]), v = __bfloat162float(p[half]);
+                float sn, cs;
+                sincosf((float)(pos0 + r / a.heads) * a.freq[i], &sn, &cs);
+                p[0] = __float2bfloat16_rn(u * cs - v * sn);
+                p[half] = __float2bfloat16_rn(v * cs + u * sn);
+            }
+            __syncthreads();
+        }
         const __nv_bfloat16* ks = kbuf[buf];
         if (active) {
             float s[8][4];
@@ -483,8 +500,8 @@ PRB_API int prb_latent_attention_mma(float* out, void* out_bf, const float* gate
                                      const float* sinks, float* ws_o, float* ws_ml, int heads,
                                      int rank, int rot_dim, int page_size, int max_pages,
                                      int num_pages, float scale, int window, int split_keys,
-                                     int splits, int kw, int ws_rows, int* status,
-                                     cudaStream_t stream) {
+                                     int splits, int kw, int ws_rows, const float* freq,
+                                     int rot_dims, int* status, cudaStream_t stream) {
     // kw = 1: 8 warps, up to 128 rows an item; kw = 4 or 2: 4 warps, 16 or 32 rows
     const int warps = kw == 1 ? 8 : 4;
     const int q_rows = 16 * warps / (kw > 0 ? kw : 1);
@@ -496,9 +513,10 @@ PRB_API int prb_latent_attention_mma(float* out, void* out_bf, const float* gate
         return PRB_E_SIZE;
     if (((uintptr_t)qa) % 16 != 0 || ((uintptr_t)cache) % 16 != 0) return PRB_E_ALIGN;
     if ((out == nullptr) == (out_bf == nullptr)) return PRB_E_ARG;
+    if (freq != nullptr && (rot_dims < 0 || rot_dims > rot_dim || rot_dims % 2 != 0)) return PRB_E_SIZE;
     LmArgs a{(const __nv_bfloat16*)qa, (const __nv_bfloat16*)cache, block_table, seq_of_token,
              positions, item_row0, item_tokens, item_count, out, (__nv_bfloat16*)out_bf, gate, gate_ld,
-             sinks, ws_o, ws_ml, ws_rows, n_items,
+             sinks, freq, rot_dims, ws_o, ws_ml, ws_rows, n_items,
              heads, rank,
              rot_dim, page_size, max_pages, num_pages, window, split_keys, splits, kw, scale,
              status};

@@ -140,9 +140,7 @@ def _declare(h: ctypes.CDLL) -> None:
                                      I, I, P, P]
     h.prb_latent_fold.argtypes = [P, P, L, P, P, P, I, I, I, I, I, I, I, I, P]
     h.prb_latent_attention_mma.argtypes = [P, P, P, L, P, P, P, P, P, P, P, P, I, P, P, P, I, I, I,
-                                           I, I, I, F, I, I, I, I, I, P, P]
-    h.prb_latent_rotate.argtypes = [P, P, L, P, P, I, I, I, I, I, I, P]
-    h.prb_latent_rotate.restype = c_int
+                                           I, I, I, F, I, I, I, I, I, P, I, P, P]
     h.prb_latent_mma_supports.argtypes = [I, I, I]
     h.prb_latent_mma_single_kw.argtypes = [I]
     h.prb_latent_mma_rows.argtypes = []
@@ -1039,26 +1037,10 @@ def latent_mma_rows() -> int:
     return int(lib().prb_latent_mma_rows())
 
 
-def latent_rotate(qa, q, positions, freq, heads: int, rank: int, rot_dim: int, rot_dims: int) -> None:
-    """qa[t, h, :] = q[t, h, :] with the last ``rot_dim`` numbers of every head rotated by the
-    token's position (the first ``rot_dims`` of them, rotate-half layout).  q float32
-    [T, >= heads * (rank + rot_dim)]; qa [T, heads, rank + rot_dim], float32 or bfloat16."""
-    what = "latent_rotate"
-    d = rank + rot_dim
-    if q.dtype != torch.float32 or q.stride(1) != 1 or q.shape[1] < heads * d:
-        raise KernelArgumentError(f"{what}: q must be float32 [T, heads * (rank + rot_dim)]")
-    _need(qa, None, "qa", what)
-    if tuple(qa.shape) != (q.shape[0], heads, d):
-        raise KernelArgumentError(f"{what}: shapes do not fit")
-    _check(lib().prb_latent_rotate(_p(qa), _p(q), q.stride(0), _p(positions), _p(freq), q.shape[0],
-                                   heads, rank, rot_dim, rot_dims, dtype_code(qa.dtype), _stream()),
-           what)
-
-
 def latent_attention_mma(out, qa, cache, block_table, seq_of_token, positions, item_row0,
                          item_tokens, item_count, n_items: int, sinks, ws_o, ws_ml, scale: float,
                          window, rank: int, split_keys: int, splits: int, kw: int, ws_rows: int,
-                         status, gate=None) -> None:
+                         status, gate=None, rotate=None) -> None:
     """The same as ``latent_attention`` on tensor cores for bfloat16 queries and cache.  Work
     items: item i is ``item_tokens[i]`` (1 if None) consecutive tokens of one request from
     token row ``item_row0[i]`` on, all heads (heads * tokens <= ``ws_rows`` <= 128); ``n_items``
@@ -1069,8 +1051,15 @@ def latent_attention_mma(out, qa, cache, block_table, seq_of_token, positions, i
     ``ws_ml`` (the same without rank, times 2) hold the partial results of the key ranges,
     which a second kernel joins into ``out``.  ``out`` is float32 [T, heads, rank], or
     bfloat16 of that shape, and then every head's rows are multiplied by sigmoid(gate[t, h])
-    when ``gate`` (float32 [T, heads], may be a column slice) is given."""
+    when ``gate`` (float32 [T, heads], may be a column slice) is given.  ``rotate`` = (freq,
+    rot_dims): the queries come unrotated and the kernel rotates the last part of every row by
+    its position as it loads them."""
     what = "latent_attention_mma"
+    freq, rot_dims = rotate if rotate is not None else (None, 0)
+    if freq is not None:
+        _need(freq, torch.float32, "freq", what)
+        if freq.numel() < rot_dims // 2:
+            raise KernelArgumentError(f"{what}: {rot_dims // 2} frequencies wanted")
     _need(out, None, "out", what)
     if out.dtype not in (torch.float32, torch.bfloat16) or (gate is not None and out.dtype != torch.bfloat16):
         raise KernelArgumentError(f"{what}: out is float32, or bfloat16 (which may take a gate)")
@@ -1103,7 +1092,8 @@ def latent_attention_mma(out, qa, cache, block_table, seq_of_token, positions, i
         _p(out) if out.dtype == torch.bfloat16 else None, _p(gate), gate_ld, _p(qa), _p(cache), _p(block_table), _p(seq_of_token), _p(positions), _p(item_row0),
         _p(item_tokens), _p(item_count), int(n_items), _p(sinks), _p(ws_o), _p(ws_ml), heads, rank,
         d - rank, page_size, block_table.shape[1], num_pages, float(scale), int(window or 0),
-        int(split_keys), int(splits), int(kw), int(ws_rows), _p(status), _stream())
+        int(split_keys), int(splits), int(kw), int(ws_rows), _p(freq), int(rot_dims), _p(status),
+        _stream())
     _check(code, what)
     if code == 0 and n_items > 0 and splits > 1:
         add_launches(1)                      # the kernel that joins the partial results

@@ -19,9 +19,9 @@ Two ways through a step.  float32 (and bfloat16 sizes the tensor-core kernel doe
 Uq, then per head the fold through Uk with the rotation, the 32-bit attention kernel, the
 unfold through Uv with the gate, the output projection.  bfloat16 on tensor cores: Uk is
 folded into Uq and Uv into the output projection when the model is built (in 32-bit, rounded
-once), so a step is the folded query product, the rotation, the attention kernel, which
-leaves the gated sums in bfloat16, and the folded output product: two kernels fewer, and
-the per-head matrices run at the products' speed.
+once), so a step is the folded query product, the attention kernel, which rotates the
+queries as it loads them and leaves the gated sums in bfloat16, and the folded output
+product: three kernels fewer, and the per-head matrices run at the products' speed.
 
 The first matrix product carries Dq, Dkv and G in one, and whatever rows an arrangement
 asks to ride along (:meth:`fuse_input_rows`); its float32 result feeds the norms unrounded.
@@ -263,19 +263,20 @@ class LatentAttention(Mixer):
                            self.kv_norm, group.slots if cache.writes else None, ctx.positions,
                            self.freq, self.q_rank, self.rank, self.rot_dim, self.rot_dims,
                            self.eps, ctx.status)
-        q = ctx.scratch("latent_q", (cap, first.n_out), torch.float32)[:t]
-        first.forward(ctx, cq, q)
         gate = self.input.view(proj, "gate") if self.head_gate else None
         width = self.rank + self.rot_dim
         if self.tensor_cores:
+            # the folded query leaves its product in bfloat16; the attention kernel rotates
+            # the rows' last parts as it loads them
             qa = ctx.scratch("latent_qa", (cap, self.heads, width), dtype)[:t]
-            ops.latent_rotate(qa, q, ctx.positions, self.freq, self.heads, self.rank, self.rot_dim,
-                              self.rot_dims)
+            first.forward(ctx, cq, qa.view(t, self.heads * width))
             gated = ctx.scratch("latent_gated", (cap, self.heads, self.rank), dtype)[:t]
             self._attend_tensor_cores(ctx, gated, qa, cache, group, gate)
             self.out_fold.forward(ctx, gated.view(t, self.heads * self.rank), x,
                                   resid=x if accumulate else None)
             return
+        q = ctx.scratch("latent_q", (cap, first.n_out), torch.float32)[:t]
+        first.forward(ctx, cq, q)
         qa = ctx.scratch("latent_qa", (cap, self.heads, width), torch.float32)[:t]
         ops.latent_fold(qa, q, self.uk, ctx.positions, self.freq, self.heads, self.dim,
                         self.rot_dim, self.rot_dims, self.rank)
@@ -314,7 +315,8 @@ class LatentAttention(Mixer):
                 lat, qa, cache.k, group.block_table, ctx.seq_of_token, ctx.positions,
                 work.arrays[rows_name], work.arrays[tokens_name] if tokens_name else None,
                 work.counts[counter], n, self.sinks, ws_o, ws_ml, self.scale, self.window,
-                self.rank, split_keys, splits, kw, ws_rows, ctx.status, gate=gate)
+                self.rank, split_keys, splits, kw, ws_rows, ctx.status, gate=gate,
+                rotate=(self.freq, self.rot_dims))
 
 
 def attend_latent(ctx, lat, qa, cache: LayerCache, group, sinks, scale: float,

@@ -271,7 +271,7 @@ class LatentCase:
         return self
 
     def run(self, queries, sinks=None, scale=1.0, window=None, kernel="generic", items=None,
-            split_keys=None):
+            split_keys=None, rotate=None):
         """queries: list of (request, position, qa [heads, rank + rot_dim]); returns
         [n, heads, rank] and the plain implementation's answer.  ``kernel``: "generic" (32-bit
         arithmetic), or the tensor-core kernel with every query an item of its own whose warps
@@ -305,7 +305,7 @@ class LatentCase:
                                      i32([i for i, _ in items] + [0, 0]),
                                      None if kernel == "single" else i32([k for _, k in items] + [1, 1]),
                                      count, len(items) + 2, sk, ws_o, ws_ml, scale, window, self.rank,
-                                     split_keys, splits, kw, ws_rows, status)
+                                     split_keys, splits, kw, ws_rows, status, rotate=rotate)
         assert int(status[0]) == 0, status.tolist()
         want = []
         for b, p, q in queries:
@@ -487,22 +487,29 @@ def test_latent_mixer_chain(dtype):
     assert torch.allclose(got, want, atol=tol, rtol=tol), float((got - want).abs().max())
 
 
-def test_rotate_kernel():
-    """The rotation alone: the last rot_dim numbers of every head, the first rot_dims of
-    them in the rotate-half layout, the rest and the head's first part untouched."""
-    from pretrained_rstr_b200.csrc import ops
-    heads, rank, rot_dim, rot_dims, t = 3, 16, 12, 8, 9
-    g = torch.Generator().manual_seed(15)
-    q = torch.randn(t, heads * (rank + rot_dim) + 4, generator=g)
-    pos = torch.tensor([0, 1, 5, 63, 64, 200, 1000, 4095, 77], dtype=torch.int32)
-    freq = torch.tensor([31.0 ** (-2.0 * i / rot_dims) for i in range(rot_dims // 2)])
-    for dtype, tol in ((torch.float32, 2e-4), (torch.bfloat16, 2e-2)):
-        qa = torch.empty(t, heads, rank + rot_dim, dtype=dtype, device=DEV)
-        ops.latent_rotate(qa, q.to(DEV), pos.to(DEV), freq.to(DEV), heads, rank, rot_dim, rot_dims)
-        src = q[:, :heads * (rank + rot_dim)].reshape(t, heads, rank + rot_dim).double()
-        want = src.clone()
-        want[..., rank:] = P.rotate(src[..., rank:], pos, 31.0, rot_dims)
-        assert torch.allclose(qa.cpu().double(), want, atol=tol, rtol=tol)
+@pytest.mark.parametrize("kernel", ["single", "tile"])
+def test_latent_attention_rotates_queries(kernel):
+    """Given unrotated queries and the rotation's frequencies, the tensor-core kernel rotates
+    the last part of every row by the row's position as it loads them: the same result as with
+    queries rotated beforehand, for rows of several tokens in one tile and for every key range."""
+    heads, rank, rot, rot_dims = 5, 32, 32, 16
+    case = LatentCase([400], rank, rot, torch.bfloat16, seed=21).to_device()
+    g = torch.Generator().manual_seed(22)
+    first, n = 250, 30
+    raw = [torch.randn(heads, rank + rot, generator=g).to(torch.bfloat16).float() for _ in range(n)]
+    freq = torch.tensor([50.0 ** (-2.0 * i / rot_dims) for i in range(rot_dims // 2)])
+    turned = []
+    for i, q in enumerate(raw):
+        t = q.clone().double()
+        t[:, rank:] = P.rotate(t[None, :, rank:], torch.tensor([first + i]), 50.0, rot_dims)[0]
+        turned.append(t.float())
+    queries = [(0, first + i, q) for i, q in enumerate(raw)]
+    items = [(r0, min(25, n - r0)) for r0 in range(0, n, 25)] if kernel == "tile" else None
+    _, want = case.run([(0, first + i, q) for i, q in enumerate(turned)], scale=0.3)
+    for split_keys in (64, 512):
+        got, _ = case.run(queries, scale=0.3, kernel=kernel, items=items, split_keys=split_keys,
+                          rotate=(freq.to(DEV), rot_dims))
+        assert torch.allclose(got, want, atol=6e-3, rtol=1e-3), float((got - want).abs().max())
 
 
 # ------------------------------------------------------- whole models through the step function
