@@ -30,8 +30,10 @@ constexpr int LU_SLICES = LU_THREADS / 32;
 
 __device__ __forceinline__ float la_sigmoid(float z) { return 1.0f / (1.0f + expf(-z)); }
 
-// One CTA per token.  proj: float32 [T, ld]; columns q_col.. hold the query latent (q_rank),
-// kv_col.. the key/value latent (rank) followed by the part to rotate (rot_dim).
+// Two CTAs per token (blockIdx.y: 0 the query latent, 1 the key/value latent and the cache row;
+// side by side, since each is a reduction and a round trip long).  proj: float32 [T, ld];
+// columns q_col.. hold the query latent (q_rank), kv_col.. the key/value latent (rank) followed
+// by the part to rotate (rot_dim).
 template <typename C, typename A>
 __global__ void __launch_bounds__(LA_THREADS)
 latent_prepare_kernel(A* __restrict__ cq, long cq_ld, C* __restrict__ cache,
@@ -46,12 +48,14 @@ latent_prepare_kernel(A* __restrict__ cq, long cq_ld, C* __restrict__ cache,
     const int t = blockIdx.x;
     if (t >= n_tokens) return;
     const float* p = proj + (size_t)t * ld;
-    if (cq != nullptr) {
+    if (blockIdx.y == 0) {
+        if (cq == nullptr) return;
         float s = 0.0f;
         for (int i = threadIdx.x; i < q_rank; i += blockDim.x) s += p[q_col + i] * p[q_col + i];
         const float inv = 1.0f / sqrtf(prb_block_sum(s, scratch) / (float)q_rank + eps);
         for (int i = threadIdx.x; i < q_rank; i += blockDim.x)
             cq[(size_t)t * cq_ld + i] = prb_from_float<A>(p[q_col + i] * inv * wq[i]);
+        return;
     }
     const int slot = slots ? slots[t] : -1;
     if (slot < 0) return;                                     // padding, or nothing to keep
@@ -307,7 +311,7 @@ PRB_API int prb_latent_prepare(void* cq, long cq_ld, void* cache, const float* p
         page_size <= 0 || (cq != nullptr && q_rank <= 0))
         return PRB_E_SIZE;
 #define PRB_LP(C, A)                                                                              \
-    latent_prepare_kernel<C, A><<<n_tokens, LA_THREADS, 0, stream>>>(                             \
+    latent_prepare_kernel<C, A><<<dim3(n_tokens, 2), LA_THREADS, 0, stream>>>(                    \
         (A*)cq, cq_ld, (C*)cache, proj, ld, q_col, kv_col, wq, wkv, slots, positions, freq,       \
         n_tokens, q_rank, rank, rot_dim, rot_dims, page_size, num_pages, eps, status)
     if (cache_dtype == PRB_F32 && act_dtype == PRB_F32) PRB_LP(float, float);

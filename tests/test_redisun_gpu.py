@@ -597,17 +597,18 @@ def test_mixed_batches_with_reuse(folders, name, dtype):
     compare(rp.rows, oracle, TOL[dtype])
 
 
+@pytest.mark.parametrize("name", ["A", "B"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_greedy_generation_entry_point(folders, dtype):
+def test_greedy_generation_entry_point(folders, name, dtype):
     """``load_lm`` / ``generate_ids`` / ``generate_batch``: the scheduler's portions, batches
     and the steps launched ahead of their token ids (the previous token lives on the device)
     choose the plain implementation's tokens."""
     from pretrained_rstr_b200 import generate_batch, generate_ids, load_lm
-    folder = folders[("A", dtype)]
+    folder = folders[(name, dtype)]
     cfg, tensors = P.read_folder(folder)
     m = load_lm(folder, gpu=True, dtype=dtype, max_lanes=3, max_batched_tokens=128,
                 prefill_chunk=32, maxpos=256)
-    prompts = list(_prompts("A", [1, 9, 33, 70, 130], salt=200).values())
+    prompts = list(_prompts(name, [1, 9, 33, 70, 130], salt=200).values())
     n_new = 12
 
     def agree(prompt, got):
