@@ -490,7 +490,6 @@ PRB_API int prb_latent_mma_supports(int heads, int rank, int rot_dim) {
 // How the warps of a CTA share single tokens: the key parts per block (4, 2 or 1).
 PRB_API int prb_latent_mma_single_kw(int heads) { return heads <= 16 ? 4 : (heads <= 32 ? 2 : 1); }
 PRB_API int prb_latent_mma_rows() { return LM_ROWS; }
-PRB_API int prb_latent_mma_max_splits() { return LM_MAX_PARTS; }
 
 PRB_API int prb_latent_attention_mma(float* out, void* out_bf, const float* gate, long gate_ld,
                                      const void* qa, const void* cache,
