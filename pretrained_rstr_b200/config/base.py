@@ -14,7 +14,9 @@ Besides sizes, a configuration answers two structural questions as *data*:
 
 ``run_order()``
     a list of :class:`RunEntry`: which layer runs when, and whose cache it uses.  A
-    layer may appear twice, and an entry may read another layer's cache.
+    layer may appear twice (with the same cache, or with one of its own per run), an entry
+    may read another layer's cache, and an entry may have the embedding's output added to the
+    stream before it.
 """
 from __future__ import annotations
 
@@ -65,13 +67,19 @@ class RunEntry:
     """One position in the execution order.
 
     ``layer``       index into ``layer_specs()`` (weights).
-    ``cache_layer`` index of the layer whose cache this entry attends over.
+    ``cache_layer`` which cache (pages and state) this entry uses: the index of the layer
+                    whose cache it is, or, for a layer that runs several times with a cache
+                    of its own each time, any further number (the entry that writes a cache
+                    says, by its ``layer``, whose mixer shapes it).
     ``writes_cache`` False when the entry only reads a cache another entry filled.
+    ``add_embedding`` the embedding's output (the stream as it was before the first entry)
+                    is added to the stream before this entry runs.
     """
 
     layer: int
     cache_layer: int
     writes_cache: bool = True
+    add_embedding: bool = False
 
 
 class ModelConfig:

@@ -37,7 +37,8 @@ class Architecture:
 
 
 _REGISTRY: Dict[str, Architecture] = {}
-_BUNDLED = ("pretrained_rstr_b200.models.gpt2", "pretrained_rstr_b200.models.redisun")
+_BUNDLED = ("pretrained_rstr_b200.models.gpt2", "pretrained_rstr_b200.models.redisun",
+            "pretrained_rstr_b200.models.pezarax")
 _bundled_loaded = False
 
 

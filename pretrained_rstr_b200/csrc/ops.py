@@ -146,6 +146,20 @@ def _declare(h: ctypes.CDLL) -> None:
     h.prb_latent_mma_rows.argtypes = []
     h.prb_latent_attention.argtypes = [P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, I, P, P]
     h.prb_latent_unfold.argtypes = [P, L, P, P, P, L, I, I, I, I, I, I, P]
+    h.prb_embed_scaled.argtypes = [P, P, P, P, I, I, I, F, I, P, P]
+    h.prb_route_scores.argtypes = [P, P, P, P, L, P, I, I, I, I, I, I, I, I, P]
+    h.prb_routed_act.argtypes = [P, L, P, L, I, I, I, P, L, I, I, I, I, P]
+    h.prb_retention_lanes.argtypes = [I]
+    h.prb_retention_scan.argtypes = [P, P, L, I, I, I, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I,
+                                     P, P]
+    h.prb_retention_finish.argtypes = [P, L, P, P, L, I, P, I, I, I, F, I, P]
+    h.prb_diff_prepare.argtypes = [P, P, P, L, I, I, I, P, P, P, I, I, I, I, I, I, I, I, I, P, P]
+    h.prb_diff_attention.argtypes = [P, L, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, F, F, F, I,
+                                     I, P, P]
+    for name in ("prb_embed_scaled", "prb_route_scores", "prb_routed_act", "prb_retention_lanes",
+                 "prb_retention_scan", "prb_retention_finish", "prb_diff_prepare",
+                 "prb_diff_attention"):
+        getattr(h, name).restype = c_int
     for name in ("prb_embed_pair", "prb_rms_norm", "prb_gated_pair", "prb_route",
                  "prb_latent_prepare", "prb_latent_fold", "prb_latent_attention",
                  "prb_latent_unfold", "prb_latent_attention_mma", "prb_latent_mma_supports",
@@ -1097,3 +1111,185 @@ def latent_attention_mma(out, qa, cache, block_table, seq_of_token, positions, i
     _check(code, what)
     if code == 0 and n_items > 0 and splits > 1:
         add_launches(1)                      # the kernel that joins the partial results
+
+
+# ------------------------------------------------- scaled embedding, routing by scores
+def embed_scaled(out, tokens, table, scale: float, keep=None, status=None) -> None:
+    """out[t] = table[tokens[t]] * scale (float32 [T, width]); ``keep`` receives the same rows
+    a second time (a stream that is joined by its own beginning again later)."""
+    what = "embed_scaled"
+    _need(out, torch.float32, "out", what)
+    _need(tokens, torch.int32, "tokens", what)
+    _need(table, None, "table", what)
+    n, width = out.shape
+    if table.shape[1] != width or tokens.numel() < n:
+        raise KernelArgumentError(f"{what}: table width or token count does not fit the output")
+    if keep is not None:
+        _need(keep, torch.float32, "keep", what)
+        if keep.shape[0] < n or keep.shape[1] != width:
+            raise KernelArgumentError(f"{what}: keep has the wrong shape")
+    _check(lib().prb_embed_scaled(_p(out), _p(keep), _p(tokens), _p(table), n, width,
+                                  table.shape[0], float(scale), dtype_code(table.dtype),
+                                  _p(status), _stream()), what)
+
+
+SCORE_CODES = {"sigmoid": 0, "identity": 1}
+ROUTED_ACT_CODES = {"relu_squared": 0, "relu": 1, "gelu_new": 2, "silu": 3}
+
+
+def route_scores(weights, chosen, chosen_w, x, w, top: int, score: str = "sigmoid",
+                 renormalize: bool = False) -> None:
+    """Router by independent scores: z = x . w^T in 32-bit (x [T, width] float32 or bfloat16; w
+    [experts, width]), or, with ``w`` None, x [T, experts] holds z already (possibly a column
+    slice of a wider tensor); s = sigmoid(z) or z; the ``top`` largest; weights float32 [T,
+    experts] hold the chosen scores (divided by their sum if ``renormalize``) and zero
+    elsewhere; chosen int32 [T, top] and chosen_w float32 [T, top] list them by rank."""
+    what = "route_scores"
+    if not x.is_cuda or x.stride(1) != 1:
+        raise KernelArgumentError(f"{what}: x must be on CUDA with unit inner stride")
+    _need(weights, torch.float32, "weights", what)
+    _need(chosen, torch.int32, "chosen", what)
+    _need(chosen_w, torch.float32, "chosen_w", what)
+    n, width = x.shape
+    experts = width if w is None else w.shape[0]
+    if w is not None:
+        _need(w, None, "w", what)
+        if w.shape[1] != width:
+            raise KernelArgumentError(f"{what}: shapes do not fit")
+    if weights.shape != (n, experts) or chosen.shape != (n, top) or chosen_w.shape != (n, top):
+        raise KernelArgumentError(f"{what}: shapes do not fit")
+    _check(lib().prb_route_scores(_p(weights), _p(chosen), _p(chosen_w), _p(x), x.stride(0), _p(w),
+                                  n, width, experts, int(top), SCORE_CODES[score],
+                                  1 if renormalize else 0, dtype_code(x.dtype),
+                                  F32 if w is None else dtype_code(w.dtype), _stream()), what)
+
+
+def routed_act(out, inp, in_col: int, n: int, weights, group: int, act: str = "relu_squared",
+               weight_on: str = "input") -> None:
+    """out[t, i] = act(weights[t, i // group] * inp[t, in_col + i]) for i < n: the activation of
+    routed experts whose weight multiplies the expert's input (inp float32: what the experts'
+    first, linear product made of the unweighted input); ``weight_on`` "output": the weight
+    times act(inp).  Zero where the weight is zero."""
+    what = "routed_act"
+    if not inp.is_cuda or inp.dtype != torch.float32 or inp.stride(1) != 1:
+        raise KernelArgumentError(f"{what}: inp must be float32 on CUDA with unit inner stride")
+    if not out.is_cuda or out.stride(1) != 1 or out.shape[0] < inp.shape[0] or n > out.shape[1] \
+            or in_col + n > inp.shape[1]:
+        raise KernelArgumentError(f"{what}: columns outside the tensors")
+    if weights.dtype != torch.float32 or weights.stride(1) != 1 or weights.shape[0] < inp.shape[0] \
+            or weights.shape[1] * group < n:
+        raise KernelArgumentError(f"{what}: weights must be float32 [rows, ceil(n / group)]")
+    _check(lib().prb_routed_act(_p(out), out.stride(0), _p(inp), inp.stride(0), int(in_col), int(n),
+                                inp.shape[0], _p(weights), weights.stride(0), int(group),
+                                ROUTED_ACT_CODES[act], 1 if weight_on == "output" else 0,
+                                dtype_code(out.dtype), _stream()), what)
+
+
+# ------------------------------------------------------------------------ retention
+def retention_lanes(dim: int) -> int:
+    """Lanes the scan spreads a state column over (0: a head size it does not take)."""
+    return int(lib().prb_retention_lanes(int(dim)))
+
+
+def retention_scan(o_raw, proj, q_col: int, k_col: int, v_col: int, state, q_start, state_slot,
+                   positions, decay, freq, n_requests: int, heads: int, dim: int, vdim: int,
+                   rot_dims: int, k_scale: float, cols: int, status=None) -> None:
+    """o_raw[t, h] = S_t^T q_t with S_t = decay_h S_(t-1) + k_t v_t^T per request and head, over
+    the step's tokens in order, from and back to ``state`` [slots, heads, vdim, dim] float32
+    (zero at position 0).  proj float32 [T, ld] holds q, k (heads * dim) and v (heads * vdim)
+    at the given columns; q and k are rotated (rotate-half, the first ``rot_dims``
+    coordinates) and k scaled by ``k_scale``.  ``cols``: value columns per CTA."""
+    what = "retention_scan"
+    _need(o_raw, torch.float32, "o_raw", what)
+    _need(state, torch.float32, "state", what)
+    _need(decay, torch.float32, "decay", what)
+    _need(freq, torch.float32, "freq", what)
+    for name, t in (("q_start", q_start), ("state_slot", state_slot), ("positions", positions)):
+        _need(t, torch.int32, name, what)
+    if not proj.is_cuda or proj.dtype != torch.float32 or proj.stride(1) != 1:
+        raise KernelArgumentError(f"{what}: proj must be float32 on CUDA with unit inner stride")
+    n = o_raw.shape[0]
+    if proj.shape[0] < n or o_raw.shape[1] != heads * vdim or decay.numel() != heads or \
+            tuple(state.shape[1:]) != (heads, vdim, dim) or q_start.numel() < n_requests + 1 or \
+            state_slot.numel() < n_requests or freq.numel() < max(1, rot_dims // 2) or \
+            max(q_col, k_col) + heads * dim > proj.shape[1] or v_col + heads * vdim > proj.shape[1]:
+        raise KernelArgumentError(f"{what}: shapes do not fit")
+    _check(lib().prb_retention_scan(_p(o_raw), _p(proj), proj.stride(0), int(q_col), int(k_col),
+                                    int(v_col), _p(state), _p(q_start), _p(state_slot),
+                                    _p(positions), _p(decay), _p(freq), n, int(n_requests),
+                                    state.shape[0], heads, dim, vdim, int(rot_dims), float(k_scale),
+                                    int(cols), _p(status), _stream()), what)
+
+
+def retention_finish(out, o_raw, proj, g_col: int, seq_of_token, heads: int, vdim: int,
+                     eps: float) -> None:
+    """out[t, h] = o_raw[t, h] / sqrt(mean(o_raw[t, h]^2) + eps) * silu(proj[t, g_col + h * vdim
+    ...]) per head; ``proj`` None: no gate.  out in the activation type, its rows may be wider
+    than heads * vdim."""
+    what = "retention_finish"
+    _need(o_raw, torch.float32, "o_raw", what)
+    _need(seq_of_token, torch.int32, "seq_of_token", what)
+    n = o_raw.shape[0]
+    if not out.is_cuda or out.stride(1) != 1 or out.shape[0] < n or out.shape[1] < heads * vdim:
+        raise KernelArgumentError(f"{what}: out has the wrong shape")
+    if proj is not None and (proj.dtype != torch.float32 or proj.stride(1) != 1 or
+                             proj.shape[0] < n or g_col + heads * vdim > proj.shape[1]):
+        raise KernelArgumentError(f"{what}: proj has the wrong shape or type")
+    _check(lib().prb_retention_finish(_p(out), out.stride(0), _p(o_raw), _p(proj),
+                                      0 if proj is None else proj.stride(0), int(g_col),
+                                      _p(seq_of_token), n, heads, vdim, float(eps),
+                                      dtype_code(out.dtype), _stream()), what)
+
+
+# --------------------------------------------------------------- differential attention
+def diff_prepare(q_out, cache, proj, q_col: int, k_col: int, v_col: int, slots, positions, freq,
+                 heads: int, kv_heads: int, dim: int, vdim: int, rot_dims: int, status=None) -> None:
+    """Rotate the two maps of every query and key head of the step (rotate-half, the first
+    ``rot_dims`` coordinates); queries go to q_out float32 [T, heads * 2 * dim], keys and
+    values to the tokens' cache rows [k map 1 | k map 2 | v] (cache: [pages, kv_heads, page
+    size, 2 * dim + vdim]; ``slots`` None: nothing is cached)."""
+    what = "diff_prepare"
+    _need(q_out, torch.float32, "q_out", what)
+    _need(cache, None, "cache", what)
+    _need(positions, torch.int32, "positions", what)
+    _need(freq, torch.float32, "freq", what)
+    if not proj.is_cuda or proj.dtype != torch.float32 or proj.stride(1) != 1:
+        raise KernelArgumentError(f"{what}: proj must be float32 on CUDA with unit inner stride")
+    n = q_out.shape[0]
+    pages, kvh, page_size, rowlen = cache.shape
+    if kvh != kv_heads or rowlen != 2 * dim + vdim or q_out.shape[1] != heads * 2 * dim or \
+            proj.shape[0] < n or q_col + heads * 2 * dim > proj.shape[1] or \
+            k_col + kv_heads * 2 * dim > proj.shape[1] or v_col + kv_heads * vdim > proj.shape[1] \
+            or freq.numel() < max(1, rot_dims // 2):
+        raise KernelArgumentError(f"{what}: shapes do not fit")
+    if slots is not None:
+        _need(slots, torch.int32, "slots", what)
+    _check(lib().prb_diff_prepare(_p(q_out), _p(cache), _p(proj), proj.stride(0), int(q_col),
+                                  int(k_col), int(v_col), _p(slots), _p(positions), _p(freq), n,
+                                  heads, kv_heads, dim, vdim, int(rot_dims), page_size, pages,
+                                  dtype_code(cache.dtype), _p(status), _stream()), what)
+
+
+def diff_attention(out, q, cache, block_table, seq_of_token, positions, heads: int, dim: int,
+                   vdim: int, block: int, scale: float, lam: float, eps: float, out_scale: float,
+                   status=None) -> None:
+    """Per (token, head): a1 - lam * a2 of two softmax attentions over the same values, then
+    unit RMS over vdim times ``out_scale``.  A query at position p sees keys floor(p / block) *
+    block .. p (``block`` 0: from 0).  32-bit arithmetic; out in the cache's type."""
+    what = "diff_attention"
+    _need(q, torch.float32, "q", what)
+    _need(cache, None, "cache", what)
+    _need(block_table, torch.int32, "block_table", what)
+    _need(seq_of_token, torch.int32, "seq_of_token", what)
+    _need(positions, torch.int32, "positions", what)
+    n = q.shape[0]
+    pages, kv_heads, page_size, rowlen = cache.shape
+    if rowlen != 2 * dim + vdim or q.shape[1] != heads * 2 * dim or out.dtype != cache.dtype or \
+            out.stride(1) != 1 or out.shape[0] < n or out.shape[1] < heads * vdim:
+        raise KernelArgumentError(f"{what}: shapes or types do not fit")
+    _check(lib().prb_diff_attention(_p(out), out.stride(0), _p(q), _p(cache), _p(block_table),
+                                    _p(seq_of_token), _p(positions), n, heads, kv_heads, dim, vdim,
+                                    page_size, block_table.shape[1], pages, int(block or 0),
+                                    float(scale), float(lam), float(eps), float(out_scale),
+                                    dtype_code(cache.dtype), dtype_code(out.dtype), _p(status),
+                                    _stream()), what)

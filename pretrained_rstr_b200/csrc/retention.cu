@@ -1,0 +1,220 @@
+// Retention: linear attention with a fixed decay per head and a running state per request,
+//     S_t = decay_h S_(t-1) + k_t v_t^T,   o_t = S_t^T q_t        (S: [dim, vdim], 32-bit)
+// with rotary positions (rotate-half layout, the first rot_dims coordinates) on q and k and
+// k scaled by `k_scale` after the rotation.  Everything that enters the recurrence is 32-bit.
+//
+// retention_scan: one CTA per (chunk of value columns, head, request).  A column of S is
+// independent of the others, so columns are spread over CTAs and over the threads of a CTA; a
+// column's `dim` numbers are spread over R neighbouring lanes (NI numbers a lane, in
+// registers) and the dot with q is closed with R - 1 shuffles.  The CTA walks its request's
+// tokens of the step in order, a block of tokens at a time: q and k of the block are rotated
+// and staged in shared memory by all threads, then every thread runs the recurrence over
+// the block.  The state comes from the request's slot (zero at position 0) and goes back
+// there after the last token, so a prompt may be cut anywhere and a decoded token is the
+// same kernel with one token.  The order of every sum depends on dim and vdim only.
+//
+// retention_finish: a warp per (token, head): unit root-mean-square over the head's vdim
+// values, times silu(gate), written in the activation type.
+#include "common.cuh"
+
+namespace {
+constexpr int RET_NI = 16;          // state numbers a lane holds per column
+constexpr int RET_BLOCK = 16;       // tokens staged at a time
+
+struct ScanArgs {
+    float* o_raw;             // [T, heads * vdim]
+    const float* proj;        // [T, ld]: q at q_col, k at k_col (heads * dim each), v at v_col
+    long ld;
+    int q_col, k_col, v_col;
+    float* state;             // [slots, heads, vdim, dim]
+    const int* q_start;       // [requests + 1]
+    const int* state_slot;    // [requests]
+    const int* positions;     // [T]
+    const float* decay;       // [heads]
+    const float* freq;        // [rot_dims / 2]
+    int n_tokens, n_slots, heads, dim, vdim, rot_dims, cols, lanes;   // lanes = R
+    float k_scale;
+    int* status;
+};
+
+__global__ void retention_scan_kernel(ScanArgs a) {
+    extern __shared__ __align__(16) float smem[];
+    prb_grid_launch_dependents();
+    const int chunk = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+    const int t0 = a.q_start[b], t1 = a.q_start[b + 1];
+    if (t1 <= t0 || t0 < 0 || t1 > a.n_tokens) return;
+    const int R = a.lanes, dim_pad = R * RET_NI;
+    float* qs = smem;                               // [RET_BLOCK][dim_pad]
+    float* ks = qs + RET_BLOCK * dim_pad;           // [RET_BLOCK][dim_pad]
+    float* vs = ks + RET_BLOCK * dim_pad;           // [RET_BLOCK][cols]
+    const int r = threadIdx.x % R, c = threadIdx.x / R;
+    const int col = chunk * a.cols + c;
+    const bool live = c < a.cols && col < a.vdim;
+    const int slot = a.state_slot[b];
+    if (slot < 0 || slot >= a.n_slots) {
+        if (threadIdx.x == 0) prb_set_status(a.status, PRB_S_SLOT_RANGE, t0, slot, a.n_slots);
+        return;
+    }
+    const int pos0 = a.positions[t0];
+    float* srow = a.state + (((size_t)slot * a.heads + h) * a.vdim + (live ? col : 0)) * a.dim;
+    float S[RET_NI];
+#pragma unroll
+    for (int ii = 0; ii < RET_NI; ++ii) {
+        const int i = r * RET_NI + ii;
+        S[ii] = (live && pos0 > 0 && i < a.dim) ? srow[i] : 0.0f;
+    }
+    const float decay = a.decay[h];
+    const int half = a.rot_dims / 2;
+    for (int tb = t0; tb < t1; tb += RET_BLOCK) {
+        const int nb = min(RET_BLOCK, t1 - tb);
+        __syncthreads();                            // the block before has been consumed
+        // stage q and k, rotated; units: pairs (i, i + half) for i < half, then single i >= rot_dims
+        const int units = half + (a.dim - a.rot_dims);
+        for (int u = threadIdx.x; u < nb * units; u += blockDim.x) {
+            const int tok = u / units, w = u - tok * units;
+            const float* row = a.proj + (size_t)(tb + tok) * a.ld;
+            const float* qr = row + a.q_col + h * a.dim;
+            const float* kr = row + a.k_col + h * a.dim;
+            if (w < half) {
+                float sn, cs;
+                sincosf((float)a.positions[tb + tok] * a.freq[w], &sn, &cs);
+                const float q0 = qr[w], q1 = qr[w + half], k0 = kr[w], k1 = kr[w + half];
+                qs[tok * dim_pad + w] = q0 * cs - q1 * sn;
+                qs[tok * dim_pad + w + half] = q1 * cs + q0 * sn;
+                ks[tok * dim_pad + w] = (k0 * cs - k1 * sn) * a.k_scale;
+                ks[tok * dim_pad + w + half] = (k1 * cs + k0 * sn) * a.k_scale;
+            } else {
+                const int i = w - half + a.rot_dims;
+                qs[tok * dim_pad + i] = qr[i];
+                ks[tok * dim_pad + i] = kr[i] * a.k_scale;
+            }
+        }
+        for (int u = threadIdx.x; u < nb * (dim_pad - a.dim); u += blockDim.x) {
+            const int tok = u / (dim_pad - a.dim), i = a.dim + u % (dim_pad - a.dim);
+            qs[tok * dim_pad + i] = 0.0f;
+            ks[tok * dim_pad + i] = 0.0f;
+        }
+        for (int u = threadIdx.x; u < nb * a.cols; u += blockDim.x) {
+            const int tok = u / a.cols, cc = u - tok * a.cols;
+            const int vc = chunk * a.cols + cc;
+            vs[tok * a.cols + cc] = vc < a.vdim
+                ? a.proj[(size_t)(tb + tok) * a.ld + a.v_col + h * a.vdim + vc] : 0.0f;
+        }
+        __syncthreads();
+        for (int tok = 0; tok < nb; ++tok) {
+            const float v = c < a.cols ? vs[tok * a.cols + c] : 0.0f;
+            const float4* q4 = reinterpret_cast<const float4*>(qs + tok * dim_pad + r * RET_NI);
+            const float4* k4 = reinterpret_cast<const float4*>(ks + tok * dim_pad + r * RET_NI);
+            float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+            for (int g = 0; g < RET_NI / 4; ++g) {
+                const float4 kk = k4[g], qq = q4[g];
+                S[4 * g + 0] = fmaf(decay, S[4 * g + 0], kk.x * v);
+                S[4 * g + 1] = fmaf(decay, S[4 * g + 1], kk.y * v);
+                S[4 * g + 2] = fmaf(decay, S[4 * g + 2], kk.z * v);
+                S[4 * g + 3] = fmaf(decay, S[4 * g + 3], kk.w * v);
+                acc[0] = fmaf(S[4 * g + 0], qq.x, acc[0]);
+                acc[1] = fmaf(S[4 * g + 1], qq.y, acc[1]);
+                acc[2] = fmaf(S[4 * g + 2], qq.z, acc[2]);
+                acc[3] = fmaf(S[4 * g + 3], qq.w, acc[3]);
+            }
+            float o = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+            for (int m = 1; m < R; m <<= 1) o += __shfl_xor_sync(0xffffffffu, o, m);
+            if (live && r == 0)
+                a.o_raw[(size_t)(tb + tok) * a.heads * a.vdim + h * a.vdim + col] = o;
+        }
+    }
+    if (live) {
+#pragma unroll
+        for (int ii = 0; ii < RET_NI; ++ii) {
+            const int i = r * RET_NI + ii;
+            if (i < a.dim) srow[i] = S[ii];
+        }
+    }
+}
+
+template <typename O>
+__global__ void retention_finish_kernel(O* __restrict__ out, long out_ld, const float* __restrict__ o_raw,
+                                        const float* __restrict__ proj, long ld, int g_col,
+                                        const int* __restrict__ seq, int n_tokens, int heads,
+                                        int vdim, float eps) {
+    prb_grid_launch_dependents();
+    const int unit = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (unit >= n_tokens * heads) return;
+    const int t = unit / heads, h = unit - t * heads;
+    O* o = out + (size_t)t * out_ld + h * vdim;
+    if (seq[t] < 0) {                               // a padding row
+        for (int j = lane; j < vdim; j += 32) o[j] = prb_from_float<O>(0.0f);
+        return;
+    }
+    const float* raw = o_raw + (size_t)t * heads * vdim + h * vdim;
+    float ss = 0.0f;
+    for (int j = lane; j < vdim; j += 32) ss = fmaf(raw[j], raw[j], ss);
+    ss = prb_warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)vdim + eps);
+    const float* g = proj ? proj + (size_t)t * ld + g_col + h * vdim : nullptr;
+    for (int j = lane; j < vdim; j += 32) {
+        float v = raw[j] * inv;
+        if (g) {
+            const float z = g[j];
+            v *= z / (1.0f + expf(-z));
+        }
+        o[j] = prb_from_float<O>(v);
+    }
+}
+}  // namespace
+
+// Lanes a column's dim numbers are spread over: the power of two >= dim / 16, at most 32.
+PRB_API int prb_retention_lanes(int dim) {
+    int r = 1;
+    while (r * RET_NI < dim) r <<= 1;
+    return r <= 32 ? r : 0;
+}
+
+PRB_API int prb_retention_scan(float* o_raw, const float* proj, long ld, int q_col, int k_col,
+                               int v_col, float* state, const int* q_start, const int* state_slot,
+                               const int* positions, const float* decay, const float* freq,
+                               int n_tokens, int n_requests, int n_slots, int heads, int dim,
+                               int vdim, int rot_dims, float k_scale, int cols, int* status,
+                               cudaStream_t stream) {
+    if (n_tokens <= 0 || n_requests <= 0) return 0;
+    const int lanes = prb_retention_lanes(dim);
+    if (heads <= 0 || heads > 65535 || n_requests > 65535 || dim <= 0 || vdim <= 0 || lanes == 0 ||
+        rot_dims < 0 || rot_dims > dim || rot_dims % 2 != 0 || cols <= 0)
+        return PRB_E_SIZE;
+    if (ld % 4 != 0 || ((uintptr_t)proj) % 16 != 0) return PRB_E_ALIGN;
+    // threads: cols * lanes rounded up to whole warps, at most 1,024
+    if (cols > vdim) cols = vdim;
+    while (cols * lanes > 1024) cols = (cols + 1) / 2;
+    const int threads = (cols * lanes + 31) / 32 * 32;
+    const int chunks = (vdim + cols - 1) / cols;
+    ScanArgs a{o_raw, proj, ld, q_col, k_col, v_col, state, q_start, state_slot, positions, decay,
+               freq, n_tokens, n_slots, heads, dim, vdim, rot_dims, cols, lanes, k_scale, status};
+    const size_t smem = (size_t)RET_BLOCK * (2 * lanes * RET_NI + cols) * sizeof(float);
+    if (smem > 48 * 1024)
+        cudaFuncSetAttribute(retention_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)smem);
+    retention_scan_kernel<<<dim3(chunks, heads, n_requests), threads, smem, stream>>>(a);
+    PRB_LAUNCH_CHECK();
+    return 0;
+}
+
+PRB_API int prb_retention_finish(void* out, long out_ld, const float* o_raw, const float* proj, long ld,
+                                 int g_col, const int* seq, int n_tokens, int heads, int vdim,
+                                 float eps, int out_dtype, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (heads <= 0 || vdim <= 0) return PRB_E_SIZE;
+    const int warps = 4;
+    const unsigned blocks = (unsigned)(((size_t)n_tokens * heads + warps - 1) / warps);
+    if (out_dtype == PRB_F32)
+        retention_finish_kernel<float><<<blocks, warps * 32, 0, stream>>>(
+            (float*)out, out_ld, o_raw, proj, ld, g_col, seq, n_tokens, heads, vdim, eps);
+    else if (out_dtype == PRB_BF16)
+        retention_finish_kernel<__nv_bfloat16><<<blocks, warps * 32, 0, stream>>>(
+            (__nv_bfloat16*)out, out_ld, o_raw, proj, ld, g_col, seq, n_tokens, heads, vdim, eps);
+    else
+        return PRB_E_DTYPE;
+    PRB_LAUNCH_CHECK();
+    return 0;
+}

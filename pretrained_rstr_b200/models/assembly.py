@@ -19,6 +19,7 @@ from typing import Dict, List, Tuple
 import torch
 
 from ..cache.manager import GroupSpec
+from ..csrc import ops
 from ..parts import build_part, part_factory
 from ..parts.interfaces import LayerCache, StateSpec
 from ..parts.linear import LazyNorm
@@ -60,14 +61,22 @@ class Model:
 
     # ---------------------------------------------------------------- cache layout
     def _derive_cache_layout(self) -> None:
-        writers = {e.cache_layer for e in self.order if e.writes_cache}
+        # a cache is shaped by the mixer of the entry that writes it (caches are numbered by
+        # layer; further numbers are the caches of layers that run several times)
+        owner: Dict[int, int] = {}
+        for e in self.order:
+            if e.writes_cache:
+                if owner.setdefault(e.cache_layer, e.layer) != e.layer:
+                    raise ValueError(f"run order: cache {e.cache_layer} is written by layers "
+                                     f"{owner[e.cache_layer]} and {e.layer}")
+        writers = set(owner)
         for e in self.order:
             if e.cache_layer not in writers:
                 raise ValueError(f"run order: layer {e.layer} reads the cache of layer "
                                  f"{e.cache_layer}, which no entry writes")
         keyed: Dict[Tuple[int, int, object], List[int]] = {}
         for layer in sorted(writers):
-            mixer = self.blocks[layer].mixer
+            mixer = self.blocks[owner[layer]].mixer
             spec = mixer.kv_spec()
             if spec is not None:
                 keyed.setdefault((spec.kv_heads, spec.head_dim, spec.window,
@@ -116,9 +125,20 @@ class Model:
         of 32 elements: copy it to keep it)."""
         t = ctx.launch_tokens
         x = ctx.scratch("residual", (ctx.token_capacity, self.width), torch.float32)[:t]
-        self.embedding.forward(ctx, self.position, x)
+        x0 = None
+        if any(e.add_embedding for e in self.order):
+            # the stream's beginning is kept for the entries that add it again
+            x0 = ctx.scratch("embedding_output", (ctx.token_capacity, self.width), torch.float32)[:t]
+        if x0 is not None and getattr(self.embedding, "keeps_copy", False):
+            self.embedding.forward(ctx, self.position, x, keep=x0)
+        else:
+            self.embedding.forward(ctx, self.position, x)
+            if x0 is not None:
+                ops.bias_act(x0, x, None, None, None)
         for entry, cache in zip(self.order, self._caches):
             block = self.blocks[entry.layer]
+            if entry.add_embedding:
+                ops.bias_act(x, x, None, x0, None)             # x += x0, in 32-bit
             block.forward(ctx, x, cache)
             ctx.last_block = block             # (a block may leave something for its successor)
             if self.tap is not None:
@@ -164,8 +184,8 @@ def build_model(config, store, runtime) -> Model:
     head = build_part("head", config.head_spec(), store, runtime)
     order = config.run_order()
     for e in order:
-        if not (0 <= e.layer < len(blocks)) or not (0 <= e.cache_layer < len(blocks)):
-            raise ValueError(f"run order names layer {e.layer}/{e.cache_layer}; "
+        if not (0 <= e.layer < len(blocks)) or e.cache_layer < 0:
+            raise ValueError(f"run order names layer {e.layer} (cache {e.cache_layer}); "
                              f"the model has {len(blocks)}")
     emb = config.embedding_spec().params
     return Model(config, runtime, embedding, position, blocks, order, final_norm, head,

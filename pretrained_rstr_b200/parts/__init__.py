@@ -1,4 +1,5 @@
-from . import attention, block, embedding, feed_forward, head, latent_attention, norms, positions  # noqa: F401  (register)
+from . import (attention, block, differential_attention, embedding, feed_forward, head,  # noqa: F401  (register)
+               latent_attention, norms, positions, retention)
 from .interfaces import (Block, Embedding, FeedForward, Head, KVSpec, LayerCache, Mixer, Norm,
                          PositionEncoding, StateSpec)
 from .linear import Linear

@@ -17,18 +17,22 @@ class PreNormBlock(Block):
     graph_safe = True
     def __init__(self, mixer: Mixer, feed_forward: FeedForward, norms: Dict[str, Norm],
                  width: int, runtime):
-        missing = {"mixer", "feed_forward"} - set(norms)
-        if missing or len(norms) != 2:
-            raise ValueError(f"pre_norm wants the norms 'mixer' and 'feed_forward', got {sorted(norms)}")
+        # (a layer without a feed-forward has the mixer's norm alone)
+        self.has_ff = not getattr(feed_forward, "is_none", False)
+        wanted = {"mixer", "feed_forward"} if self.has_ff else {"mixer"}
+        if set(norms) != wanted:
+            raise ValueError(f"pre_norm wants the norms {sorted(wanted)}, got {sorted(norms)}")
         self.mixer, self.feed_forward = mixer, feed_forward
         self.norms = dict(norms)
-        self.mixer_norm, self.feed_forward_norm = norms["mixer"], norms["feed_forward"]
+        self.mixer_norm, self.feed_forward_norm = norms["mixer"], norms.get("feed_forward")
         self.width, self.runtime = width, runtime
 
     def forward(self, ctx, x, cache: LayerCache) -> None:
         t = x.shape[0]
         h = ctx.scratch("block_normed", (ctx.token_capacity, self.width), self.runtime.dtype)[:t]
         self.mixer.forward(ctx, self._normed(ctx, self.mixer, self.mixer_norm, x, h), x, cache)
+        if not self.has_ff:
+            return
         self.feed_forward.forward(
             ctx, self._normed(ctx, self.feed_forward, self.feed_forward_norm, x, h), x)
 

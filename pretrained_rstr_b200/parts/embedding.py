@@ -23,6 +23,25 @@ class TokenEmbedding(Embedding):
         ops.embed(x, ctx.tokens, ctx.positions, self.table, position.table(), ctx.status)
 
 
+class ScaledTokenEmbedding(Embedding):
+    """x[t] = table[token[t]] * scale.  ``keeps_copy``: the rows can be left a second time in
+    ``keep`` (for a run order that adds the embedding's output to the stream again)."""
+    graph_safe = True
+    keeps_copy = True
+
+    def __init__(self, table: torch.Tensor, vocab: int, width: int, scale: float, runtime):
+        if tuple(table.shape) != (vocab, width):
+            raise ValueError(f"scaled_token_embedding: table is {list(table.shape)}, "
+                             f"expected [{vocab}, {width}]")
+        self.table = table.to(runtime.dtype).contiguous()
+        self.vocab, self.width, self.scale = vocab, width, float(scale)
+
+    def forward(self, ctx, position, x, keep=None) -> None:
+        if position.table() is not None:
+            raise ValueError("scaled_token_embedding adds no position table")
+        ops.embed_scaled(x, ctx.tokens, self.table, self.scale, keep=keep, status=ctx.status)
+
+
 class TokenPairEmbedding(Embedding):
     """x[t] = table[token] + pairs[row]: a second table indexed by a hash of (previous token,
     token), row = (prev * mul_prev + token * mul_cur) mod buckets; a sequence's first token
@@ -61,6 +80,9 @@ register_part("embedding", "token_embedding",
               lambda p, store, rt: TokenEmbedding(
                   store.get(p["weights"] + p.get("suffix", ".weight"), rt.dtype),
                   p["vocab"], p["width"], rt))
+register_part("embedding", "scaled_token_embedding",
+              lambda p, store, rt: ScaledTokenEmbedding(
+                  store.get(p["weights"], rt.dtype), p["vocab"], p["width"], p["scale"], rt))
 register_part("embedding", "token_pair_embedding",
               lambda p, store, rt: TokenPairEmbedding(
                   store.get(p["table"], rt.dtype), store.get(p["pairs"], rt.dtype), p["vocab"],

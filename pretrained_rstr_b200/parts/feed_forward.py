@@ -160,6 +160,70 @@ class GatedMoE(FeedForward):
         self.down.forward(ctx, a, x, resid=x if accumulate else None)
 
 
+class RoutedExperts(FeedForward):
+    """``experts`` small feed-forwards down(act(up(.))) without biases, of which a token uses
+    the ``top`` with the largest scores s = sigmoid(router h) (``score``; router logits are
+    32-bit accumulators).  The weights are the chosen scores themselves (``renormalize``:
+    divided by their sum) and multiply the expert's INPUT (``weight_on`` "input": the result
+    is the sum of expert(w h)) or its output.
+
+    All experts' up rows and the router's are ONE matrix product (up is linear: up(w h) =
+    w up(h), so the weight meets the 32-bit result inside the activation); activations of
+    experts a token did not choose are zero, and one product with all down matrices side by
+    side sums the chosen experts.  Every token pays for every expert's arithmetic: right at any
+    sizes, cheap while experts are small."""
+    graph_safe = True
+    can_overwrite = True
+
+    def __init__(self, p: dict, store, runtime):
+        from .latent_attention import FusedInput
+        width, n, inner = int(p["width"]), int(p["experts"]), int(p["inner"])
+        self.width, self.experts, self.top, self.inner = width, n, int(p["top"]), inner
+        self.activation = p.get("activation", "relu_squared")
+        self.score = p.get("score", "sigmoid")
+        self.renormalize = bool(p.get("renormalize", False))
+        self.weight_on = p.get("weight_on", "input")
+        if self.activation not in ops.ROUTED_ACT_CODES or self.score not in ops.SCORE_CODES or \
+                self.weight_on not in ("input", "output"):
+            raise ValueError("routed_experts: unknown activation, score or weight placement")
+        if not 1 <= self.top <= n:
+            raise ValueError(f"routed_experts: top {self.top} of {n} experts")
+        self.runtime = runtime
+        pre = p["prefix"]
+
+        def need(name, shape):
+            t = store.get(pre + name)
+            if tuple(t.shape) != tuple(shape):
+                raise ValueError(f"{pre + name}: expected {list(shape)}, found {list(t.shape)}")
+            return t
+
+        self.input = FusedInput(width, runtime, "routed_in")
+        self.input.add("up", torch.cat([need(f"e{e}.up", (inner, width)) for e in range(n)]))
+        self.input.add("router", need("router", (n, width)))
+        self.down = padded_linear(
+            torch.cat([need(f"e{e}.down", (width, inner)) for e in range(n)], dim=1), runtime)
+
+    def fuse_input_rows(self, name: str, weight) -> str:
+        return self.input.add(name, weight)
+
+    def fused_rows(self, name: str):
+        return self.input.view(self._proj, name)
+
+    def forward(self, ctx, h, x, accumulate: bool = True) -> None:
+        t = x.shape[0]
+        cap = ctx.token_capacity
+        proj = self._proj = self.input.run(ctx, h)
+        weights = ctx.scratch("routed_weights", (cap, self.experts), torch.float32)[:t]
+        chosen = ctx.scratch("routed_chosen", (cap, self.top), torch.int32)[:t]
+        chosen_w = ctx.scratch("routed_chosen_w", (cap, self.top), torch.float32)[:t]
+        ops.route_scores(weights, chosen, chosen_w, self.input.view(proj, "router"), None,
+                         self.top, self.score, self.renormalize)
+        a = ctx.scratch_zero("routed_act", (cap, self.down.n_in), self.runtime.dtype)[:t]
+        ops.routed_act(a, proj, self.input.cols["up"][0], self.experts * self.inner, weights,
+                       self.inner, self.activation, self.weight_on)
+        self.down.forward(ctx, a, x, resid=x if accumulate else None)
+
+
 def _gated_mlp(p, store, rt) -> GatedMLP:
     w = p["weights"]
     return GatedMLP(store.get(w["gate"]), store.get(w["up"]), store.get(w["down"]), p["width"],
@@ -170,4 +234,5 @@ def _gated_mlp(p, store, rt) -> GatedMLP:
 register_part("feed_forward", "dense_mlp", _dense_mlp)
 register_part("feed_forward", "gated_mlp", _gated_mlp)
 register_part("feed_forward", "gated_moe", lambda p, store, rt: GatedMoE(p, store, rt))
+register_part("feed_forward", "routed_experts", lambda p, store, rt: RoutedExperts(p, store, rt))
 register_part("feed_forward", "none", lambda p, store, rt: NoFeedForward())

@@ -58,8 +58,14 @@ class RMSNorm(Norm):
 
 
 def _rms_norm(params, store, runtime) -> RMSNorm:
+    """``scale`` (optional): a constant the result is multiplied by (a head that scales its
+    logits has the constant here, in the 32-bit weight, instead of a pass over the logits)."""
     gain = store.get(params["gain"]) if params.get("gain") else None
     weight = store.get(params["weight"]) if params.get("weight") else None
+    scale = float(params.get("scale", 1.0))
+    if scale != 1.0:
+        weight = (torch.ones(params["size"], dtype=torch.float32, device=runtime.device)
+                  if weight is None else weight.to(torch.float32)) * scale
     return RMSNorm(gain, weight, params["eps"], params["size"])
 
 
