@@ -79,6 +79,39 @@ def chunk_mask(t: int, size: int, start: int = 0) -> torch.Tensor:
     return (p[None, :] <= p[:, None]) & ((p[None, :] // size) == (p[:, None] // size))
 
 
+def two_map_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask: torch.Tensor,
+                      scale: float, lam: float, eps: float, factor: float) -> torch.Tensor:
+    """q [T, heads, 2, dim] (rotated), k [S, groups, 2, dim], v [S, groups, vdim], mask [T, S]
+    -> [T, heads, vdim]: a1 - lam a2, unit RMS per head, times ``factor``."""
+    t, heads = q.shape[0], q.shape[1]
+    per = heads // k.shape[1]
+    out = torch.zeros((t, heads, v.shape[-1]), dtype=q.dtype)
+    for hd in range(heads):
+        g = hd // per
+        maps = []
+        for m in range(2):
+            s = (q[:, hd, m] @ k[:, g, m].T) * scale
+            s = s.masked_fill(~mask, float("-inf"))
+            maps.append(torch.softmax(s, dim=-1) @ v[:, g])
+        out[:, hd] = unit_rms(maps[0] - lam * maps[1], eps) * factor
+    return out
+
+
+def decayed_states(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay, state=None):
+    """q, k [T, heads, dim], v [T, heads, vdim] -> (o [T, heads, vdim], last state [heads, dim,
+    vdim]) with S <- decay_h S + k v^T and o = S^T q, token by token."""
+    t, heads, dim = q.shape
+    out = torch.zeros((t, heads, v.shape[-1]), dtype=q.dtype)
+    last = torch.zeros((heads, dim, v.shape[-1]), dtype=q.dtype) if state is None else state.clone()
+    for hd in range(heads):
+        s = last[hd]
+        for i in range(t):
+            s = float(decay[hd]) * s + torch.outer(k[i, hd], v[i, hd])
+            out[i, hd] = s.T @ q[i, hd]
+        last[hd] = s
+    return out, last
+
+
 def differential_attention(h: torch.Tensor, tensors, prefix: str, mx: dict, eps: float,
                            start: int = 0) -> torch.Tensor:
     """Two softmax attentions per head over the same values, subtracted with one learned
@@ -97,24 +130,19 @@ def differential_attention(h: torch.Tensor, tensors, prefix: str, mx: dict, eps:
     q = rotate_half(q, pos, float(mx["rot"]["base"]), int(mx["rot"]["dims"]))
     k = rotate_half(k, pos, float(mx["rot"]["base"]), int(mx["rot"]["dims"]))
     lam = torch.exp((w("lq1") * w("lk1")).sum()) - torch.exp((w("lq2") * w("lk2")).sum()) + diff
-    mask = chunk_mask(t, int(mx["mask"]["size"]), start)
-    out = torch.zeros((t, heads, vdim), dtype=dtype)
-    per = heads // groups
-    for hd in range(heads):
-        g = hd // per
-        maps = []
-        for m in range(2):
-            s = (q[:, hd, m] @ k[:, g, m].T) * float(mx["scale"])
-            s = s.masked_fill(~mask, float("-inf"))
-            maps.append(torch.softmax(s, dim=-1) @ v[:, g])
-        o = maps[0] - lam * maps[1]
-        out[:, hd] = unit_rms(o, eps) * (1.0 - diff)
+    size = int(mx["mask"]["size"]) if mx.get("mask") else start + t
+    mask = chunk_mask(t, size, start)
+    out = two_map_attention(q, k, v, mask, float(mx["scale"]), float(lam), eps, 1.0 - diff)
     return out.reshape(t, heads * vdim) @ w("o").T
 
 
-def retention(h: torch.Tensor, tensors, prefix: str, mx: dict, eps: float) -> torch.Tensor:
+def retention(h: torch.Tensor, tensors, prefix: str, mx: dict, eps: float,
+              delicate: Optional[list] = None) -> torch.Tensor:
     """Linear attention with one fixed decay per head, token by token:
-    S <- decay S + k v^T, o = S^T q; unit RMS per head, a SiLU gate of the input, projection."""
+    S <- decay S + k v^T, o = S^T q; unit RMS per head, a SiLU gate of the input, projection.
+    ``delicate`` (a list) receives a tensor [T]: per token the smallest, over heads, of rms(o)
+    over the size o would have if nothing cancelled (|q_t| sqrt(sum_j decay^(2(t-j)) |k_j|^2
+    mean(v_j^2))); where that is tiny the unit norm blows rounding up, the sign of o included."""
     dtype = h.dtype
     w = lambda name: tensors[prefix + "mix." + name].to(dtype)
     t = h.shape[0]
@@ -125,13 +153,16 @@ def retention(h: torch.Tensor, tensors, prefix: str, mx: dict, eps: float) -> to
     v = (h @ w("v").T).reshape(t, heads, vdim)
     q = rotate_half(q, pos, float(mx["rot"]["base"]), int(mx["rot"]["dims"]))
     k = rotate_half(k, pos, float(mx["rot"]["base"]), int(mx["rot"]["dims"])) * dim ** -0.5
-    out = torch.zeros((t, heads, vdim), dtype=dtype)
-    for hd in range(heads):
-        decay = float(mx["decay"][hd])
-        state = torch.zeros((dim, vdim), dtype=dtype)
-        for i in range(t):
-            state = decay * state + torch.outer(k[i, hd], v[i, hd])
-            out[i, hd] = state.T @ q[i, hd]
+    out, _ = decayed_states(q, k, v, mx["decay"])
+    if delicate is not None:
+        ratios = torch.zeros((t, heads), dtype=dtype)
+        for hd in range(heads):
+            acc = 0.0
+            for i in range(t):
+                acc = float(mx["decay"][hd]) ** 2 * acc + float(k[i, hd].pow(2).sum() * v[i, hd].pow(2).mean())
+                size = float(q[i, hd].norm()) * math.sqrt(acc)
+                ratios[i, hd] = float(out[i, hd].pow(2).mean().sqrt()) / max(size, 1e-300)
+        delicate.append(ratios.min(dim=1).values)
     out = unit_rms(out, eps).reshape(t, heads * vdim)
     gate = h @ w("g").T
     return (out * gate * torch.sigmoid(gate)) @ w("o").T
@@ -140,18 +171,20 @@ def retention(h: torch.Tensor, tensors, prefix: str, mx: dict, eps: float) -> to
 def routed_experts(h: torch.Tensor, tensors, prefix: str, mlp: dict,
                    margins: Optional[list] = None) -> torch.Tensor:
     """Sigmoid scores per expert; the ``top`` largest are chosen and weight the expert's
-    INPUT; an expert is down(relu(up(.))^2).  ``margins`` (a list) receives, per token, the gap
-    between the last chosen score and the best one left out."""
+    INPUT; an expert is down(relu(up(.))^2).  ``margins`` (a list) receives a tensor [T]: per token the gap
+    between the router logits of the last expert chosen and the best one left out."""
     dtype = h.dtype
     w = lambda name: tensors[prefix + "mlp." + name].to(dtype)
     n, top = int(mlp["router"]["experts"]), int(mlp["router"]["top"])
-    scores = torch.sigmoid(h @ w("router").T)
+    logits = h @ w("router").T
+    scores = torch.sigmoid(logits)
     order = torch.argsort(scores, dim=-1, descending=True, stable=True)
     out = torch.zeros_like(h)
+    if margins is not None:
+        ranked = torch.gather(logits, 1, order)
+        margins.append(ranked[:, top - 1] - ranked[:, top] if top < n
+                       else torch.full((h.shape[0],), float("inf"), dtype=dtype))
     for i in range(h.shape[0]):
-        if margins is not None:
-            ranked = scores[i, order[i]]
-            margins.append(float(ranked[top - 1] - ranked[top]) if top < n else float("inf"))
         for e in order[i, :top].tolist():
             u = (scores[i, e] * h[i]) @ w(f"e{e}.up").T
             out[i] += (torch.relu(u) ** 2) @ w(f"e{e}.down").T
@@ -174,9 +207,9 @@ def run_order(cfg: dict) -> List[tuple]:
 
 
 def forward(tokens: List[int], tensors, cfg: dict, dtype=torch.float64, taps: Optional[list] = None,
-            margins: Optional[list] = None) -> torch.Tensor:
+            margins: Optional[list] = None, delicate: Optional[list] = None) -> torch.Tensor:
     """Logits [T, vocab] of one whole sequence.  ``taps`` receives the stream after every
-    layer run."""
+    layer run; ``margins`` and ``delicate``: see ``routed_experts`` and ``retention``."""
     eps = float(cfg["norm"]["eps"])
     x0 = embed(tokens, tensors, cfg, dtype)
     x = x0.clone()
@@ -188,7 +221,7 @@ def forward(tokens: List[int], tensors, cfg: dict, dtype=torch.float64, taps: Op
         if entry["type"] == "attention":
             x = x + differential_attention(h, tensors, p, entry["mixer"], eps)
         elif entry["type"] == "retention":
-            x = x + retention(h, tensors, p, entry["mixer"], eps)
+            x = x + retention(h, tensors, p, entry["mixer"], eps, delicate)
         else:
             raise ValueError(f"unknown mixer {entry['type']!r}")
         if entry.get("mlp") is not None:
@@ -198,3 +231,13 @@ def forward(tokens: List[int], tensors, cfg: dict, dtype=torch.float64, taps: Op
             taps.append(x.clone())
     x = weighted_norm(x, tensors["final.norm"], eps)
     return (x @ tensors["head"].to(dtype).T) * float(cfg["logit_scale"])
+
+
+def greedy(prompt: List[int], n_new: int, tensors, cfg: dict, dtype=torch.float64) -> List[int]:
+    """The ``n_new`` tokens greedy decoding appends, each from a whole new forward pass."""
+    ids, out = list(prompt), []
+    for _ in range(n_new):
+        nxt = int(forward(ids, tensors, cfg, dtype)[-1].argmax())
+        out.append(nxt)
+        ids.append(nxt)
+    return out
