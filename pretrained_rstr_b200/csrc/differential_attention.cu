@@ -233,6 +233,173 @@ diff_attention_kernel(O* __restrict__ out, long out_ld, const float* __restrict_
         if (kg == 0 && jj < vdim) o[jj] = prb_from_float<O>(mine[x] * inv);
     }
 }
+// ---------------------------------------------------------------------- the tiled kernel
+// A CTA takes up to `tq` consecutive token rows of the step and ONE key/value head; the
+// HG = heads / kv_heads query heads that share it ride together, so a key's row is fetched
+// once for tq * HG (query, head) pairs.  Keys go in blocks of 32 ABSOLUTE positions (block m
+// holds positions 32 m .. 32 m + 31, whatever the tile or the portion of the prompt), staged
+// in shared memory as 32-bit numbers by coalesced loads; a warp owns up to DT_PPW pairs
+// (pair x * DT_WARPS + warp: a single token's few pairs go to a warp each), a
+// lane one key of the block for the two scores and vdim / 32 value coordinates for the sums.
+// Running maxima and sums per map, 32-bit.  Which keys meet in which partial sum depends on
+// absolute positions only: a query's result does not depend on the tile it falls in.
+constexpr int DT_WARPS = 8;
+constexpr int DT_PPW = 4;            // (query, head) pairs a warp owns
+constexpr int DT_VC = 4;             // value coordinates a lane owns at most (vdim <= 128)
+constexpr int DT_KB = 32;            // keys per block
+
+template <typename C, typename O>
+__global__ void __launch_bounds__(DT_WARPS * 32)
+diff_attention_tile_kernel(O* __restrict__ out, long out_ld, const float* __restrict__ q,
+                           const C* __restrict__ cache, const int* __restrict__ block_table,
+                           const int* __restrict__ seq_of_token, const int* __restrict__ positions,
+                           int n_tokens, int heads, int kv_heads, int dim, int vdim, int page_size,
+                           int max_pages, int num_pages, int block, int tq, float scale,
+                           float lambda, float eps, float out_scale, int* status) {
+    extern __shared__ __align__(16) float smem[];
+    prb_grid_launch_dependents();
+    const int hg = heads / kv_heads;
+    const int g = blockIdx.y;
+    const int rowlen = 2 * dim + vdim;
+    const int kpitch = 2 * dim + 1;                  // odd: lanes read their own key's row
+    float* Ks = smem;                                // [DT_KB][kpitch]
+    float* Vs = Ks + DT_KB * kpitch;                 // [DT_KB][vdim]
+    float* Qs = Vs + DT_KB * vdim;                   // [DT_WARPS * DT_PPW][2 * dim]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int r_begin = blockIdx.x * tq;
+    const int r_end = min(n_tokens, r_begin + tq);
+    int r = r_begin;
+    while (r < r_end) {
+        const int b = seq_of_token[r];
+        if (b < 0) {                                 // a padding row
+            for (int j = threadIdx.x; j < hg * vdim; j += blockDim.x)
+                out[(size_t)r * out_ld + (size_t)g * hg * vdim + j] = prb_from_float<O>(0.0f);
+            ++r;
+            continue;
+        }
+        const int p0 = positions[r];
+        int r1 = r;
+        while (r1 + 1 < r_end && seq_of_token[r1 + 1] == b && positions[r1 + 1] == p0 + (r1 + 1 - r)) ++r1;
+        const int nq = r1 - r + 1;
+        const int p_last = p0 + nq - 1;
+        if (p0 < 0 || p_last >= max_pages * page_size) {
+            if (threadIdx.x == 0) prb_set_status(status, PRB_S_POSITION_RANGE, r, p_last, max_pages * page_size);
+            for (int j = threadIdx.x; j < nq * hg * vdim; j += blockDim.x) {
+                const int qi = j / (hg * vdim), rest = j - qi * hg * vdim;
+                out[(size_t)(r + qi) * out_ld + (size_t)g * hg * vdim + rest] = prb_from_float<O>(0.0f);
+            }
+            r = r1 + 1;
+            continue;
+        }
+        const int lo_min = block > 0 ? (p0 / block) * block : 0;
+        const int* table = block_table + (size_t)b * max_pages;
+        __syncthreads();                             // the pass before is done with shared memory
+        // queries of this pass, scaled: pair = qi * hg + hh
+        const int n_pairs = nq * hg;
+        for (int e = threadIdx.x; e < n_pairs * 2 * dim; e += blockDim.x) {
+            const int pair = e / (2 * dim), d = e - pair * 2 * dim;
+            const int qi = pair / hg, hh = pair - qi * hg;
+            Qs[pair * 2 * dim + d] = q[((size_t)(r + qi) * heads + g * hg + hh) * 2 * dim + d] * scale;
+        }
+        float acc1[DT_PPW][DT_VC], acc2[DT_PPW][DT_VC];
+        float m1[DT_PPW], m2[DT_PPW], l1[DT_PPW], l2[DT_PPW];
+#pragma unroll
+        for (int x = 0; x < DT_PPW; ++x) {
+            m1[x] = m2[x] = -INFINITY;
+            l1[x] = l2[x] = 0.0f;
+#pragma unroll
+            for (int c = 0; c < DT_VC; ++c) acc1[x][c] = acc2[x][c] = 0.0f;
+        }
+        for (int j0 = (lo_min / DT_KB) * DT_KB; j0 <= p_last; j0 += DT_KB) {
+            __syncthreads();                         // the block before has been consumed
+            for (int e = threadIdx.x; e < DT_KB * rowlen; e += blockDim.x) {
+                const int kk = e / rowlen, off = e - kk * rowlen;
+                const int j = j0 + kk;
+                float val = 0.0f;
+                if (j >= lo_min && j <= p_last) {
+                    const int page = table[j / page_size];
+                    if (page < 0 || page >= num_pages) {
+                        if (off == 0) prb_set_status(status, PRB_S_PAGE_RANGE, r, j, page);
+                    } else {
+                        val = prb_to_float<C>(cache[(((size_t)page * kv_heads + g) * page_size +
+                                                    (j % page_size)) * rowlen + off]);
+                    }
+                }
+                if (off < 2 * dim) Ks[kk * kpitch + off] = val;
+                else Vs[kk * vdim + off - 2 * dim] = val;
+            }
+            __syncthreads();
+            const int j = j0 + lane;
+            const float* krow = Ks + lane * kpitch;
+#pragma unroll
+            for (int x = 0; x < DT_PPW; ++x) {
+                const int pair = x * DT_WARPS + warp;        // (few pairs spread over the warps)
+                if (pair >= n_pairs) break;
+                const int qi = pair / hg;
+                const int pi = p0 + qi;
+                const int lo = block > 0 ? (pi / block) * block : 0;
+                if (j0 > pi || j0 + DT_KB <= lo) continue;       // nothing of this block is seen
+                const bool vis = j >= lo && j <= pi;
+                const float* qrow = Qs + pair * 2 * dim;
+                float s1 = 0.0f, s2 = 0.0f;
+                for (int d = 0; d < dim; ++d) {
+                    s1 = fmaf(qrow[d], krow[d], s1);
+                    s2 = fmaf(qrow[dim + d], krow[dim + d], s2);
+                }
+                s1 = vis ? s1 : -INFINITY;
+                s2 = vis ? s2 : -INFINITY;
+                const float n1 = fmaxf(m1[x], prb_warp_max(s1)), n2 = fmaxf(m2[x], prb_warp_max(s2));
+                const float f1 = expf(m1[x] - n1), f2 = expf(m2[x] - n2);    // (exp(-inf) = 0)
+                const float e1 = vis ? expf(s1 - n1) : 0.0f, e2 = vis ? expf(s2 - n2) : 0.0f;
+                l1[x] = l1[x] * f1 + prb_warp_sum(e1);
+                l2[x] = l2[x] * f2 + prb_warp_sum(e2);
+                m1[x] = n1;
+                m2[x] = n2;
+#pragma unroll
+                for (int c = 0; c < DT_VC; ++c) {
+                    acc1[x][c] *= f1;
+                    acc2[x][c] *= f2;
+                }
+                const int k_hi = min(DT_KB, pi - j0 + 1);
+                for (int kk = 0; kk < k_hi; ++kk) {
+                    const float w1 = __shfl_sync(0xffffffffu, e1, kk), w2 = __shfl_sync(0xffffffffu, e2, kk);
+#pragma unroll
+                    for (int c = 0; c < DT_VC; ++c) {
+                        const int col = lane + 32 * c;
+                        if (col < vdim) {
+                            const float v = Vs[kk * vdim + col];
+                            acc1[x][c] = fmaf(w1, v, acc1[x][c]);
+                            acc2[x][c] = fmaf(w2, v, acc2[x][c]);
+                        }
+                    }
+                }
+            }
+        }
+        // combine the maps, unit RMS over the head, write
+#pragma unroll
+        for (int x = 0; x < DT_PPW; ++x) {
+            const int pair = x * DT_WARPS + warp;        // (few pairs spread over the warps)
+            if (pair >= n_pairs) break;
+            const int qi = pair / hg, hh = pair - qi * hg;
+            float o[DT_VC];
+            float ss = 0.0f;
+#pragma unroll
+            for (int c = 0; c < DT_VC; ++c) {
+                const float a1 = l1[x] > 0.0f ? acc1[x][c] / l1[x] : 0.0f;
+                const float a2 = l2[x] > 0.0f ? acc2[x][c] / l2[x] : 0.0f;
+                o[c] = (lane + 32 * c < vdim) ? a1 - lambda * a2 : 0.0f;
+                ss = fmaf(o[c], o[c], ss);
+            }
+            ss = prb_warp_sum(ss);
+            const float inv = out_scale / sqrtf(ss / (float)vdim + eps);
+            O* dst = out + (size_t)(r + qi) * out_ld + (size_t)(g * hg + hh) * vdim;
+#pragma unroll
+            for (int c = 0; c < DT_VC; ++c)
+                if (lane + 32 * c < vdim) dst[lane + 32 * c] = prb_from_float<O>(o[c] * inv);
+        }
+        r = r1 + 1;
+    }
+}
 }  // namespace
 
 PRB_API int prb_diff_prepare(float* q_out, void* cache, const float* proj, long ld, int q_col,
@@ -282,6 +449,47 @@ PRB_API int prb_diff_attention(void* out, long out_ld, const float* q, const voi
     else if (cache_dtype == PRB_BF16 && out_dtype == PRB_BF16) DIFF(__nv_bfloat16, __nv_bfloat16);
     else return PRB_E_DTYPE;
 #undef DIFF
+    PRB_LAUNCH_CHECK();
+    return 0;
+}
+
+// Rows a CTA of the tiled kernel takes (0: sizes it does not take; the kernel above runs then).
+PRB_API int prb_diff_attention_tile_rows(int heads, int kv_heads, int dim, int vdim) {
+    if (heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0) return 0;
+    const int hg = heads / kv_heads;
+    if (vdim > 32 * DT_VC || hg > DT_WARPS * DT_PPW || dim > 256) return 0;
+    const size_t smem = (size_t)(DT_KB * (2 * dim + 1) + DT_KB * vdim + DT_WARPS * DT_PPW * 2 * dim) * sizeof(float);
+    if (smem > 160 * 1024) return 0;
+    return (DT_WARPS * DT_PPW) / hg;
+}
+
+PRB_API int prb_diff_attention_tile(void* out, long out_ld, const float* q, const void* cache,
+                                    const int* block_table, const int* seq_of_token,
+                                    const int* positions, int n_tokens, int heads, int kv_heads,
+                                    int dim, int vdim, int page_size, int max_pages, int num_pages,
+                                    int block, int tq, float scale, float lambda, float eps,
+                                    float out_scale, int cache_dtype, int out_dtype, int* status,
+                                    cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    const int most = prb_diff_attention_tile_rows(heads, kv_heads, dim, vdim);
+    if (most <= 0 || kv_heads > 65535 || page_size <= 0 || max_pages <= 0 || block < 0) return PRB_E_SIZE;
+    if (tq <= 0 || tq > most) tq = most;
+    const size_t smem = (size_t)(DT_KB * (2 * dim + 1) + DT_KB * vdim + DT_WARPS * DT_PPW * 2 * dim) * sizeof(float);
+    dim3 grid((n_tokens + tq - 1) / tq, kv_heads);
+#define DIFFT(CT, OT)                                                                            \
+    do {                                                                                         \
+        if (smem > 48 * 1024)                                                                    \
+            cudaFuncSetAttribute(diff_attention_tile_kernel<CT, OT>,                             \
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);        \
+        diff_attention_tile_kernel<CT, OT><<<grid, DT_WARPS * 32, smem, stream>>>(               \
+            (OT*)out, out_ld, q, (const CT*)cache, block_table, seq_of_token, positions,         \
+            n_tokens, heads, kv_heads, dim, vdim, page_size, max_pages, num_pages, block, tq,    \
+            scale, lambda, eps, out_scale, status);                                              \
+    } while (0)
+    if (cache_dtype == PRB_F32 && out_dtype == PRB_F32) DIFFT(float, float);
+    else if (cache_dtype == PRB_BF16 && out_dtype == PRB_BF16) DIFFT(__nv_bfloat16, __nv_bfloat16);
+    else return PRB_E_DTYPE;
+#undef DIFFT
     PRB_LAUNCH_CHECK();
     return 0;
 }

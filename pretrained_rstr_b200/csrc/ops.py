@@ -156,6 +156,11 @@ def _declare(h: ctypes.CDLL) -> None:
     h.prb_diff_prepare.argtypes = [P, P, P, L, I, I, I, P, P, P, I, I, I, I, I, I, I, I, I, P, P]
     h.prb_diff_attention.argtypes = [P, L, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, F, F, F, I,
                                      I, P, P]
+    h.prb_diff_attention_tile_rows.argtypes = [I, I, I, I]
+    h.prb_diff_attention_tile_rows.restype = c_int
+    h.prb_diff_attention_tile.argtypes = [P, L, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, F,
+                                          F, F, I, I, P, P]
+    h.prb_diff_attention_tile.restype = c_int
     for name in ("prb_embed_scaled", "prb_route_scores", "prb_routed_act", "prb_retention_lanes",
                  "prb_retention_scan", "prb_retention_finish", "prb_diff_prepare",
                  "prb_diff_attention"):
@@ -1197,8 +1202,9 @@ def retention_scan(o_raw, proj, q_col: int, k_col: int, v_col: int, state, q_sta
     """o_raw[t, h] = S_t^T q_t with S_t = decay_h S_(t-1) + k_t v_t^T per request and head, over
     the step's tokens in order, from and back to ``state`` [slots, heads, vdim, dim] float32
     (zero at position 0).  proj float32 [T, ld] holds q, k (heads * dim) and v (heads * vdim)
-    at the given columns; q and k are rotated (rotate-half, the first ``rot_dims``
-    coordinates) and k scaled by ``k_scale``.  ``cols``: value columns per CTA."""
+    at the given columns; q and k are first rotated IN PLACE in ``proj`` (rotate-half, the first
+    ``rot_dims`` coordinates; one launch for all tokens) and k scaled by ``k_scale``.  ``cols``:
+    value columns per CTA."""
     what = "retention_scan"
     _need(o_raw, torch.float32, "o_raw", what)
     _need(state, torch.float32, "state", what)
@@ -1219,6 +1225,8 @@ def retention_scan(o_raw, proj, q_col: int, k_col: int, v_col: int, state, q_sta
                                     _p(positions), _p(decay), _p(freq), n, int(n_requests),
                                     state.shape[0], heads, dim, vdim, int(rot_dims), float(k_scale),
                                     int(cols), _p(status), _stream()), what)
+    if rot_dims > 0 or float(k_scale) != 1.0:
+        add_launches(1)                                # (the rotation is a launch of its own)
 
 
 def retention_finish(out, o_raw, proj, g_col: int, seq_of_token, heads: int, vdim: int,
@@ -1270,12 +1278,20 @@ def diff_prepare(q_out, cache, proj, q_col: int, k_col: int, v_col: int, slots, 
                                   dtype_code(cache.dtype), _p(status), _stream()), what)
 
 
+def diff_attention_tile_rows(heads: int, kv_heads: int, dim: int, vdim: int) -> int:
+    """Most token rows a CTA of the tiled kernel takes; 0: sizes only the kernel of a CTA per
+    (token, head) takes (value heads wider than 128, more than 32 query heads a key head)."""
+    return int(lib().prb_diff_attention_tile_rows(heads, kv_heads, dim, vdim))
+
+
 def diff_attention(out, q, cache, block_table, seq_of_token, positions, heads: int, dim: int,
                    vdim: int, block: int, scale: float, lam: float, eps: float, out_scale: float,
-                   status=None) -> None:
+                   status=None, tile_rows: int = 0) -> None:
     """Per (token, head): a1 - lam * a2 of two softmax attentions over the same values, then
     unit RMS over vdim times ``out_scale``.  A query at position p sees keys floor(p / block) *
-    block .. p (``block`` 0: from 0).  32-bit arithmetic; out in the cache's type."""
+    block .. p (``block`` 0: from 0).  32-bit arithmetic; out in the cache's type.
+    ``tile_rows`` > 0: the tiled kernel, a CTA per (that many consecutive token rows, key/value
+    head), keys staged in shared memory once for all of them; 0: a CTA per (token, head)."""
     what = "diff_attention"
     _need(q, torch.float32, "q", what)
     _need(cache, None, "cache", what)
@@ -1287,6 +1303,14 @@ def diff_attention(out, q, cache, block_table, seq_of_token, positions, heads: i
     if rowlen != 2 * dim + vdim or q.shape[1] != heads * 2 * dim or out.dtype != cache.dtype or \
             out.stride(1) != 1 or out.shape[0] < n or out.shape[1] < heads * vdim:
         raise KernelArgumentError(f"{what}: shapes or types do not fit")
+    if tile_rows > 0:
+        _check(lib().prb_diff_attention_tile(
+            _p(out), out.stride(0), _p(q), _p(cache), _p(block_table), _p(seq_of_token),
+            _p(positions), n, heads, kv_heads, dim, vdim, page_size, block_table.shape[1], pages,
+            int(block or 0), int(tile_rows), float(scale), float(lam), float(eps),
+            float(out_scale), dtype_code(cache.dtype), dtype_code(out.dtype), _p(status),
+            _stream()), what)
+        return
     _check(lib().prb_diff_attention(_p(out), out.stride(0), _p(q), _p(cache), _p(block_table),
                                     _p(seq_of_token), _p(positions), n, heads, kv_heads, dim, vdim,
                                     page_size, block_table.shape[1], pages, int(block or 0),

@@ -7,9 +7,9 @@
 // independent of the others, so columns are spread over CTAs and over the threads of a CTA; a
 // column's `dim` numbers are spread over R neighbouring lanes (NI numbers a lane, in
 // registers) and the dot with q is closed with R - 1 shuffles.  The CTA walks its request's
-// tokens of the step in order, a block of tokens at a time: q and k of the block are rotated
-// and staged in shared memory by all threads, then every thread runs the recurrence over
-// the block.  The state comes from the request's slot (zero at position 0) and goes back
+// tokens of the step in order, a block of tokens at a time: q and k of the block (rotated
+// beforehand, for all tokens at once, by retention_rotate) are staged in shared memory by all
+// threads, then every thread runs the recurrence over the block.  The state comes from the request's slot (zero at position 0) and goes back
 // there after the last token, so a prompt may be cut anywhere and a decoded token is the
 // same kernel with one token.  The order of every sum depends on dim and vdim only.
 //
@@ -18,8 +18,9 @@
 #include "common.cuh"
 
 namespace {
-constexpr int RET_NI = 16;          // state numbers a lane holds per column
 constexpr int RET_BLOCK = 16;       // tokens staged at a time
+// State numbers a lane holds per column: 4 for heads of up to 128 (a column over up to 32
+// lanes: many short chains, which is what hides the recurrence's latency), 16 beyond.
 
 struct ScanArgs {
     float* o_raw;             // [T, heads * vdim]
@@ -31,12 +32,44 @@ struct ScanArgs {
     const int* state_slot;    // [requests]
     const int* positions;     // [T]
     const float* decay;       // [heads]
-    const float* freq;        // [rot_dims / 2]
-    int n_tokens, n_slots, heads, dim, vdim, rot_dims, cols, lanes;   // lanes = R
-    float k_scale;
+    int n_tokens, n_slots, heads, dim, vdim, cols, lanes;   // lanes = R
     int* status;
 };
 
+// q and k of every token of the step, in place in the projection's 32-bit result: the first
+// rot_dims coordinates of every head turned by the token's position (rotate-half layout), k
+// times k_scale afterwards.  A CTA per token.
+__global__ void retention_rotate_kernel(float* __restrict__ proj, long ld, int q_col, int k_col,
+                                        const int* __restrict__ positions,
+                                        const float* __restrict__ freq, int n_tokens, int heads,
+                                        int dim, int rot_dims, float k_scale) {
+    prb_grid_launch_dependents();
+    const int t = blockIdx.x;
+    if (t >= n_tokens) return;
+    float* row = proj + (size_t)t * ld;
+    const float pos = (float)positions[t];
+    const int half = rot_dims / 2;
+    const int units = half + (dim - rot_dims);
+    for (int u = threadIdx.x; u < heads * units; u += blockDim.x) {
+        const int h = u / units, w = u - h * units;
+        float* qr = row + q_col + h * dim;
+        float* kr = row + k_col + h * dim;
+        if (w < half) {
+            float sn, cs;
+            sincosf(pos * freq[w], &sn, &cs);
+            const float q0 = qr[w], q1 = qr[w + half], k0 = kr[w], k1 = kr[w + half];
+            qr[w] = q0 * cs - q1 * sn;
+            qr[w + half] = q1 * cs + q0 * sn;
+            kr[w] = (k0 * cs - k1 * sn) * k_scale;
+            kr[w + half] = (k1 * cs + k0 * sn) * k_scale;
+        } else {
+            const int i = w - half + rot_dims;
+            kr[i] *= k_scale;
+        }
+    }
+}
+
+template <int RET_NI>
 __global__ void retention_scan_kernel(ScanArgs a) {
     extern __shared__ __align__(16) float smem[];
     prb_grid_launch_dependents();
@@ -64,30 +97,14 @@ __global__ void retention_scan_kernel(ScanArgs a) {
         S[ii] = (live && pos0 > 0 && i < a.dim) ? srow[i] : 0.0f;
     }
     const float decay = a.decay[h];
-    const int half = a.rot_dims / 2;
     for (int tb = t0; tb < t1; tb += RET_BLOCK) {
         const int nb = min(RET_BLOCK, t1 - tb);
         __syncthreads();                            // the block before has been consumed
-        // stage q and k, rotated; units: pairs (i, i + half) for i < half, then single i >= rot_dims
-        const int units = half + (a.dim - a.rot_dims);
-        for (int u = threadIdx.x; u < nb * units; u += blockDim.x) {
-            const int tok = u / units, w = u - tok * units;
-            const float* row = a.proj + (size_t)(tb + tok) * a.ld;
-            const float* qr = row + a.q_col + h * a.dim;
-            const float* kr = row + a.k_col + h * a.dim;
-            if (w < half) {
-                float sn, cs;
-                sincosf((float)a.positions[tb + tok] * a.freq[w], &sn, &cs);
-                const float q0 = qr[w], q1 = qr[w + half], k0 = kr[w], k1 = kr[w + half];
-                qs[tok * dim_pad + w] = q0 * cs - q1 * sn;
-                qs[tok * dim_pad + w + half] = q1 * cs + q0 * sn;
-                ks[tok * dim_pad + w] = (k0 * cs - k1 * sn) * a.k_scale;
-                ks[tok * dim_pad + w + half] = (k1 * cs + k0 * sn) * a.k_scale;
-            } else {
-                const int i = w - half + a.rot_dims;
-                qs[tok * dim_pad + i] = qr[i];
-                ks[tok * dim_pad + i] = kr[i] * a.k_scale;
-            }
+        for (int u = threadIdx.x; u < nb * a.dim; u += blockDim.x) {
+            const int tok = u / a.dim, i = u - tok * a.dim;
+            const float* row = a.proj + (size_t)(tb + tok) * a.ld + h * a.dim + i;
+            qs[tok * dim_pad + i] = row[a.q_col];
+            ks[tok * dim_pad + i] = row[a.k_col];
         }
         for (int u = threadIdx.x; u < nb * (dim_pad - a.dim); u += blockDim.x) {
             const int tok = u / (dim_pad - a.dim), i = a.dim + u % (dim_pad - a.dim);
@@ -101,13 +118,14 @@ __global__ void retention_scan_kernel(ScanArgs a) {
                 ? a.proj[(size_t)(tb + tok) * a.ld + a.v_col + h * a.vdim + vc] : 0.0f;
         }
         __syncthreads();
+#pragma unroll 4
         for (int tok = 0; tok < nb; ++tok) {
             const float v = c < a.cols ? vs[tok * a.cols + c] : 0.0f;
             const float4* q4 = reinterpret_cast<const float4*>(qs + tok * dim_pad + r * RET_NI);
             const float4* k4 = reinterpret_cast<const float4*>(ks + tok * dim_pad + r * RET_NI);
             float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-            for (int g = 0; g < RET_NI / 4; ++g) {
+            for (int g = 0; g < RET_NI / 4; ++g) {      // (sums in an order that dim alone fixes)
                 const float4 kk = k4[g], qq = q4[g];
                 S[4 * g + 0] = fmaf(decay, S[4 * g + 0], kk.x * v);
                 S[4 * g + 1] = fmaf(decay, S[4 * g + 1], kk.y * v);
@@ -165,14 +183,19 @@ __global__ void retention_finish_kernel(O* __restrict__ out, long out_ld, const 
 }
 }  // namespace
 
-// Lanes a column's dim numbers are spread over: the power of two >= dim / 16, at most 32.
+// State numbers a lane holds, and lanes a column's dim numbers are spread over (0: a head size
+// the scan does not take).
+static int ret_ni(int dim) { return dim <= 128 ? 4 : 16; }
 PRB_API int prb_retention_lanes(int dim) {
+    if (dim <= 0) return 0;
+    const int ni = ret_ni(dim);
     int r = 1;
-    while (r * RET_NI < dim) r <<= 1;
+    while (r * ni < dim) r <<= 1;
     return r <= 32 ? r : 0;
 }
 
-PRB_API int prb_retention_scan(float* o_raw, const float* proj, long ld, int q_col, int k_col,
+// Rotates q and k IN PLACE in `proj` (and scales k), then runs the scan.
+PRB_API int prb_retention_scan(float* o_raw, float* proj, long ld, int q_col, int k_col,
                                int v_col, float* state, const int* q_start, const int* state_slot,
                                const int* positions, const float* decay, const float* freq,
                                int n_tokens, int n_requests, int n_slots, int heads, int dim,
@@ -184,18 +207,31 @@ PRB_API int prb_retention_scan(float* o_raw, const float* proj, long ld, int q_c
         rot_dims < 0 || rot_dims > dim || rot_dims % 2 != 0 || cols <= 0)
         return PRB_E_SIZE;
     if (ld % 4 != 0 || ((uintptr_t)proj) % 16 != 0) return PRB_E_ALIGN;
+    if (rot_dims > 0 || k_scale != 1.0f) {
+        const int work = heads * (dim - rot_dims / 2);
+        const int rt = work >= 256 ? 256 : ((work + 31) / 32) * 32;
+        retention_rotate_kernel<<<n_tokens, rt, 0, stream>>>(proj, ld, q_col, k_col, positions, freq,
+                                                             n_tokens, heads, dim, rot_dims, k_scale);
+        PRB_LAUNCH_CHECK();
+    }
     // threads: cols * lanes rounded up to whole warps, at most 1,024
     if (cols > vdim) cols = vdim;
     while (cols * lanes > 1024) cols = (cols + 1) / 2;
     const int threads = (cols * lanes + 31) / 32 * 32;
     const int chunks = (vdim + cols - 1) / cols;
+    const int ni = ret_ni(dim);
     ScanArgs a{o_raw, proj, ld, q_col, k_col, v_col, state, q_start, state_slot, positions, decay,
-               freq, n_tokens, n_slots, heads, dim, vdim, rot_dims, cols, lanes, k_scale, status};
-    const size_t smem = (size_t)RET_BLOCK * (2 * lanes * RET_NI + cols) * sizeof(float);
-    if (smem > 48 * 1024)
-        cudaFuncSetAttribute(retention_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (int)smem);
-    retention_scan_kernel<<<dim3(chunks, heads, n_requests), threads, smem, stream>>>(a);
+               n_tokens, n_slots, heads, dim, vdim, cols, lanes, status};
+    const size_t smem = (size_t)RET_BLOCK * (2 * lanes * ni + cols) * sizeof(float);
+    const dim3 grid(chunks, heads, n_requests);
+    if (ni == 4) {
+        retention_scan_kernel<4><<<grid, threads, smem, stream>>>(a);
+    } else {
+        if (smem > 48 * 1024)
+            cudaFuncSetAttribute(retention_scan_kernel<16>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        retention_scan_kernel<16><<<grid, threads, smem, stream>>>(a);
+    }
     PRB_LAUNCH_CHECK();
     return 0;
 }

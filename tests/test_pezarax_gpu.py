@@ -341,8 +341,9 @@ class DiffCase:
                 cache[pg, :, :m] = self.rows[b][li * page:li * page + m].transpose(0, 1)
         self.cache, self.table = cache.to(dtype).to(DEV), table.to(DEV)
 
-    def run(self, queries, heads, block, scale, lam, eps, factor):
-        """queries: (request, position, q [heads, 2, dim]); returns kernel and plain results."""
+    def run(self, queries, heads, block, scale, lam, eps, factor, tile_rows=0):
+        """queries: (request, position, q [heads, 2, dim]); returns kernel and plain results.
+        ``tile_rows``: 0 the kernel of a CTA per (token, head), else the tiled kernel."""
         from pretrained_rstr_b200.csrc import ops
         n = len(queries)
         q = torch.stack([x for _, _, x in queries]).reshape(n, -1).to(DEV).contiguous()
@@ -350,7 +351,7 @@ class DiffCase:
         status = torch.zeros(4, dtype=torch.int32, device=DEV)
         ops.diff_attention(out, q, self.cache, self.table, _i32([b for b, _, _ in queries]),
                            _i32([p for _, p, _ in queries]), heads, self.dim, self.vdim, block,
-                           scale, lam, eps, factor, status)
+                           scale, lam, eps, factor, status, tile_rows=tile_rows)
         assert int(status[0]) == 0, status.tolist()
         want = []
         for b, p, x in queries:
@@ -366,9 +367,12 @@ class DiffCase:
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("block", [0, 20, 64, 300])
-def test_differential_attention_kernel(dtype, block):
+@pytest.mark.parametrize("tile_rows", [0, 1, 5, 10])
+def test_differential_attention_kernel(dtype, block, tile_rows):
     """Random rows; queries at the first tokens, at page borders and on both sides of every
-    block border; blocks shorter and longer than a page and than the kernel's key segment."""
+    block border; blocks shorter and longer than a page and than the kernel's key segment; a
+    CTA per (token, head), and tiles of rows that may hold runs of consecutive positions, single
+    tokens and several requests."""
     heads, kv_heads, dim, vdim = 6, 2, 24, 40
     case = DiffCase([1, 65, 200, 700], kv_heads, dim, vdim, dtype, seed=4)
     g = torch.Generator().manual_seed(8)
@@ -377,13 +381,14 @@ def test_differential_attention_kernel(dtype, block):
         places |= {m * block + o for m in range(1, 700 // block + 1) for o in (-1, 0, 1)}
     queries = [(b, p, torch.randn(heads, 2, dim, generator=g))
                for b, n in enumerate([1, 65, 200, 700]) for p in sorted(places) if p < n]
-    got, want = case.run(queries, heads, block, 0.3, 0.7, 1e-6, 0.8)
+    got, want = case.run(queries, heads, block, 0.3, 0.7, 1e-6, 0.8, tile_rows=tile_rows)
     tol = 2e-5 if dtype == torch.float32 else 2e-2
     assert torch.allclose(got, want, atol=tol, rtol=tol)
 
 
+@pytest.mark.parametrize("tile_rows", [0, 4])
 @pytest.mark.parametrize("block", [0, 50, 300])
-def test_differential_attention_edges_stand_out(block):
+def test_differential_attention_edges_stand_out(block, tile_rows):
     """A key made to dominate map 1 at the first position of a block, and one at the last
     position of the block before: the query just after sees the first and not the second; far
     keys among hundreds count when no block hides them."""
@@ -408,7 +413,7 @@ def test_differential_attention_edges_stand_out(block):
         x = torch.randn(heads, 2, dim, generator=g) * 0.1
         x[:, 0] = direction * 6.0
         queries.append((0, p, x))
-    got, want = case.run(queries, heads, block, 1.0, 0.5, 1e-6, 1.0)
+    got, want = case.run(queries, heads, block, 1.0, 0.5, 1e-6, 1.0, tile_rows=tile_rows)
     assert torch.allclose(got, want, atol=2e-5, rtol=2e-5)
     inside = [i for i, (_, p, _) in enumerate(queries) if not block or p // block == edge // block]
     assert inside and all(float(want[i].mean()) > 0.5 for i in inside)     # the edge key carries it
