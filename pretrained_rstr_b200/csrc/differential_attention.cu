@@ -257,6 +257,7 @@ diff_attention_tile_kernel(O* __restrict__ out, long out_ld, const float* __rest
                            int max_pages, int num_pages, int block, int tq, float scale,
                            float lambda, float eps, float out_scale, int* status) {
     extern __shared__ __align__(16) float smem[];
+    __shared__ int pages_s[DT_KB];
     prb_grid_launch_dependents();
     const int hg = heads / kv_heads;
     const int g = blockIdx.y;
@@ -312,21 +313,47 @@ diff_attention_tile_kernel(O* __restrict__ out, long out_ld, const float* __rest
         }
         for (int j0 = (lo_min / DT_KB) * DT_KB; j0 <= p_last; j0 += DT_KB) {
             __syncthreads();                         // the block before has been consumed
-            for (int e = threadIdx.x; e < DT_KB * rowlen; e += blockDim.x) {
-                const int kk = e / rowlen, off = e - kk * rowlen;
-                const int j = j0 + kk;
-                float val = 0.0f;
-                if (j >= lo_min && j <= p_last) {
-                    const int page = table[j / page_size];
-                    if (page < 0 || page >= num_pages) {
-                        if (off == 0) prb_set_status(status, PRB_S_PAGE_RANGE, r, j, page);
-                    } else {
-                        val = prb_to_float<C>(cache[(((size_t)page * kv_heads + g) * page_size +
-                                                    (j % page_size)) * rowlen + off]);
+            // one page look-up per key, then the rows in 16-byte pieces (or element by element
+            // where a row is no whole number of pieces): no load waits for another
+            if (threadIdx.x < DT_KB) {
+                const int jj = j0 + (int)threadIdx.x;
+                int pg = -1;
+                if (jj >= lo_min && jj <= p_last) {
+                    pg = table[jj / page_size];
+                    if (pg < 0 || pg >= num_pages) {
+                        prb_set_status(status, PRB_S_PAGE_RANGE, r, jj, pg);
+                        pg = -1;
                     }
                 }
-                if (off < 2 * dim) Ks[kk * kpitch + off] = val;
-                else Vs[kk * vdim + off - 2 * dim] = val;
+                pages_s[threadIdx.x] = pg;
+            }
+            __syncthreads();
+            constexpr int VE = 16 / (int)sizeof(C);
+            if (rowlen % VE == 0 && (2 * dim) % VE == 0) {
+                const int nv = rowlen / VE;
+#pragma unroll 2
+                for (int e = threadIdx.x; e < DT_KB * nv; e += blockDim.x) {
+                    const int kk = e / nv, vi = e - kk * nv;
+                    const int pg = pages_s[kk];
+                    uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+                    if (pg >= 0)
+                        raw = *reinterpret_cast<const uint4*>(
+                            cache + (((size_t)pg * kv_heads + g) * page_size + ((j0 + kk) % page_size)) * rowlen + vi * VE);
+                    const C* vals = reinterpret_cast<const C*>(&raw);
+                    const int off = vi * VE;
+                    float* dst = off < 2 * dim ? Ks + kk * kpitch + off : Vs + kk * vdim + off - 2 * dim;
+#pragma unroll
+                    for (int x = 0; x < VE; ++x) dst[x] = prb_to_float<C>(vals[x]);
+                }
+            } else {
+                for (int e = threadIdx.x; e < DT_KB * rowlen; e += blockDim.x) {
+                    const int kk = e / rowlen, off = e - kk * rowlen;
+                    const int pg = pages_s[kk];
+                    const float val = pg < 0 ? 0.0f : prb_to_float<C>(
+                        cache[(((size_t)pg * kv_heads + g) * page_size + ((j0 + kk) % page_size)) * rowlen + off]);
+                    if (off < 2 * dim) Ks[kk * kpitch + off] = val;
+                    else Vs[kk * vdim + off - 2 * dim] = val;
+                }
             }
             __syncthreads();
             const int j = j0 + lane;
@@ -398,6 +425,203 @@ diff_attention_tile_kernel(O* __restrict__ out, long out_ld, const float* __rest
                 if (lane + 32 * c < vdim) dst[lane + 32 * c] = prb_from_float<O>(o[c] * inv);
         }
         r = r1 + 1;
+    }
+}
+// ------------------------------------------------------------ single tokens (decoding)
+// A CTA per (token, key/value head); its few (query head) pairs ride together.  Keys go in
+// super-blocks of nw * 32 ABSOLUTE positions, staged at once by all warps; warp w then takes the
+// 32 keys w * 32 .. of the super-block for every pair, with a running state of its own, and the
+// warps' states are joined in warp order at the end.  The order of every sum depends on
+// absolute positions and nw only (nw: from the sizes alone).
+template <typename C, typename O>
+__global__ void __launch_bounds__(DT_WARPS * 32)
+diff_attention_single_kernel(O* __restrict__ out, long out_ld, const float* __restrict__ q,
+                             const C* __restrict__ cache, const int* __restrict__ block_table,
+                             const int* __restrict__ seq_of_token, const int* __restrict__ positions,
+                             int n_tokens, int heads, int kv_heads, int dim, int vdim, int page_size,
+                             int max_pages, int num_pages, int block, float scale, float lambda,
+                             float eps, float out_scale, int* status) {
+    extern __shared__ __align__(16) float smem[];
+    __shared__ int pages_s[DT_WARPS * DT_KB];
+    prb_grid_launch_dependents();
+    const int nw = blockDim.x >> 5;
+    const int hg = heads / kv_heads;                 // <= DT_PPW
+    const int g = blockIdx.y, t = blockIdx.x;
+    if (t >= n_tokens) return;
+    const int rowlen = 2 * dim + vdim;
+    const int kpitch = 2 * dim + 1;
+    const int span = nw * DT_KB;
+    float* Ks = smem;                                // [span][kpitch]
+    float* Vs = Ks + span * kpitch;                  // [span][vdim]
+    float* Qs = Vs + span * vdim;                    // [hg][2 * dim]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int b = seq_of_token[t];
+    const int pos = positions[t];
+    if (b < 0 || pos < 0 || pos >= max_pages * page_size) {
+        if (b >= 0 && threadIdx.x == 0)
+            prb_set_status(status, PRB_S_POSITION_RANGE, t, pos, max_pages * page_size);
+        for (int j = threadIdx.x; j < hg * vdim; j += blockDim.x)
+            out[(size_t)t * out_ld + (size_t)g * hg * vdim + j] = prb_from_float<O>(0.0f);
+        return;
+    }
+    const int lo = block > 0 ? (pos / block) * block : 0;
+    const int* table = block_table + (size_t)b * max_pages;
+    for (int e = threadIdx.x; e < hg * 2 * dim; e += blockDim.x)
+        Qs[e] = q[((size_t)t * heads + g * hg) * 2 * dim + e] * scale;
+    float acc1[DT_PPW][DT_VC], acc2[DT_PPW][DT_VC];
+    float m1[DT_PPW], m2[DT_PPW], l1[DT_PPW], l2[DT_PPW];
+#pragma unroll
+    for (int x = 0; x < DT_PPW; ++x) {
+        m1[x] = m2[x] = -INFINITY;
+        l1[x] = l2[x] = 0.0f;
+#pragma unroll
+        for (int c = 0; c < DT_VC; ++c) acc1[x][c] = acc2[x][c] = 0.0f;
+    }
+    for (int j0 = (lo / span) * span; j0 <= pos; j0 += span) {
+        __syncthreads();
+        for (int kk = threadIdx.x; kk < span; kk += blockDim.x) {
+            const int jj = j0 + kk;
+            int pg = -1;
+            if (jj >= lo && jj <= pos) {
+                pg = table[jj / page_size];
+                if (pg < 0 || pg >= num_pages) {
+                    prb_set_status(status, PRB_S_PAGE_RANGE, t, jj, pg);
+                    pg = -1;
+                }
+            }
+            pages_s[kk] = pg;
+        }
+        __syncthreads();
+        constexpr int VE = 16 / (int)sizeof(C);
+        if (rowlen % VE == 0 && (2 * dim) % VE == 0) {
+            const int nv = rowlen / VE;
+#pragma unroll 4
+            for (int e = threadIdx.x; e < span * nv; e += blockDim.x) {
+                const int kk = e / nv, vi = e - kk * nv;
+                const int pg = pages_s[kk];
+                uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+                if (pg >= 0)
+                    raw = *reinterpret_cast<const uint4*>(
+                        cache + (((size_t)pg * kv_heads + g) * page_size + ((j0 + kk) % page_size)) * rowlen + vi * VE);
+                const C* vals = reinterpret_cast<const C*>(&raw);
+                const int off = vi * VE;
+                float* dst = off < 2 * dim ? Ks + kk * kpitch + off : Vs + kk * vdim + off - 2 * dim;
+#pragma unroll
+                for (int x = 0; x < VE; ++x) dst[x] = prb_to_float<C>(vals[x]);
+            }
+        } else {
+            for (int e = threadIdx.x; e < span * rowlen; e += blockDim.x) {
+                const int kk = e / rowlen, off = e - kk * rowlen;
+                const int pg = pages_s[kk];
+                const float val = pg < 0 ? 0.0f : prb_to_float<C>(
+                    cache[(((size_t)pg * kv_heads + g) * page_size + ((j0 + kk) % page_size)) * rowlen + off]);
+                if (off < 2 * dim) Ks[kk * kpitch + off] = val;
+                else Vs[kk * vdim + off - 2 * dim] = val;
+            }
+        }
+        __syncthreads();
+        const int jb = j0 + warp * DT_KB;            // this warp's 32 keys
+        if (jb > pos || jb + DT_KB <= lo) continue;
+        const int j = jb + lane;
+        const bool vis = j >= lo && j <= pos;
+        const float* krow = Ks + (warp * DT_KB + lane) * kpitch;
+        const float* vblk = Vs + (size_t)warp * DT_KB * vdim;
+        const int k_hi = min(DT_KB, pos - jb + 1);
+#pragma unroll
+        for (int x = 0; x < DT_PPW; ++x) {
+            if (x >= hg) break;
+            const float* qrow = Qs + x * 2 * dim;
+            float s1 = 0.0f, s2 = 0.0f;
+            for (int d = 0; d < dim; ++d) {
+                s1 = fmaf(qrow[d], krow[d], s1);
+                s2 = fmaf(qrow[dim + d], krow[dim + d], s2);
+            }
+            s1 = vis ? s1 : -INFINITY;
+            s2 = vis ? s2 : -INFINITY;
+            const float n1 = fmaxf(m1[x], prb_warp_max(s1)), n2 = fmaxf(m2[x], prb_warp_max(s2));
+            const float f1 = expf(m1[x] - n1), f2 = expf(m2[x] - n2);
+            const float e1 = vis ? expf(s1 - n1) : 0.0f, e2 = vis ? expf(s2 - n2) : 0.0f;
+            l1[x] = l1[x] * f1 + prb_warp_sum(e1);
+            l2[x] = l2[x] * f2 + prb_warp_sum(e2);
+            m1[x] = n1;
+            m2[x] = n2;
+#pragma unroll
+            for (int c = 0; c < DT_VC; ++c) {
+                acc1[x][c] *= f1;
+                acc2[x][c] *= f2;
+            }
+            for (int kk = 0; kk < k_hi; ++kk) {
+                const float w1 = __shfl_sync(0xffffffffu, e1, kk), w2 = __shfl_sync(0xffffffffu, e2, kk);
+#pragma unroll
+                for (int c = 0; c < DT_VC; ++c) {
+                    const int col = lane + 32 * c;
+                    if (col < vdim) {
+                        const float v = vblk[kk * vdim + col];
+                        acc1[x][c] = fmaf(w1, v, acc1[x][c]);
+                        acc2[x][c] = fmaf(w2, v, acc2[x][c]);
+                    }
+                }
+            }
+        }
+    }
+    // join the warps' states in warp order: [warp][pair][m1, l1, m2, l2, acc1[vdim], acc2[vdim]]
+    __syncthreads();
+    const int rec = 4 + 2 * vdim;
+    float* J = smem;
+#pragma unroll
+    for (int x = 0; x < DT_PPW; ++x) {
+        if (x >= hg) break;
+        float* mine = J + ((size_t)warp * hg + x) * rec;
+        if (lane == 0) {
+            mine[0] = m1[x]; mine[1] = l1[x]; mine[2] = m2[x]; mine[3] = l2[x];
+        }
+#pragma unroll
+        for (int c = 0; c < DT_VC; ++c)
+            if (lane + 32 * c < vdim) {
+                mine[4 + lane + 32 * c] = acc1[x][c];
+                mine[4 + vdim + lane + 32 * c] = acc2[x][c];
+            }
+    }
+    __syncthreads();
+    if (warp < hg) {
+        const int x = warp;
+        float M1 = -INFINITY, M2 = -INFINITY;
+        for (int w = 0; w < nw; ++w) {
+            const float* rcd = J + ((size_t)w * hg + x) * rec;
+            M1 = fmaxf(M1, rcd[0]);
+            M2 = fmaxf(M2, rcd[2]);
+        }
+        float L1 = 0.0f, L2 = 0.0f, a1[DT_VC], a2[DT_VC];
+#pragma unroll
+        for (int c = 0; c < DT_VC; ++c) a1[c] = a2[c] = 0.0f;
+        for (int w = 0; w < nw; ++w) {
+            const float* rcd = J + ((size_t)w * hg + x) * rec;
+            const float f1 = rcd[0] == -INFINITY ? 0.0f : expf(rcd[0] - M1);
+            const float f2 = rcd[2] == -INFINITY ? 0.0f : expf(rcd[2] - M2);
+            L1 = fmaf(rcd[1], f1, L1);
+            L2 = fmaf(rcd[3], f2, L2);
+#pragma unroll
+            for (int c = 0; c < DT_VC; ++c)
+                if (lane + 32 * c < vdim) {
+                    a1[c] = fmaf(rcd[4 + lane + 32 * c], f1, a1[c]);
+                    a2[c] = fmaf(rcd[4 + vdim + lane + 32 * c], f2, a2[c]);
+                }
+        }
+        float o[DT_VC];
+        float ss = 0.0f;
+#pragma unroll
+        for (int c = 0; c < DT_VC; ++c) {
+            const float u1 = L1 > 0.0f ? a1[c] / L1 : 0.0f;
+            const float u2 = L2 > 0.0f ? a2[c] / L2 : 0.0f;
+            o[c] = (lane + 32 * c < vdim) ? u1 - lambda * u2 : 0.0f;
+            ss = fmaf(o[c], o[c], ss);
+        }
+        ss = prb_warp_sum(ss);
+        const float inv = out_scale / sqrtf(ss / (float)vdim + eps);
+        O* dst = out + (size_t)t * out_ld + (size_t)(g * hg + x) * vdim;
+#pragma unroll
+        for (int c = 0; c < DT_VC; ++c)
+            if (lane + 32 * c < vdim) dst[lane + 32 * c] = prb_from_float<O>(o[c] * inv);
     }
 }
 }  // namespace
@@ -490,6 +714,52 @@ PRB_API int prb_diff_attention_tile(void* out, long out_ld, const float* q, cons
     else if (cache_dtype == PRB_BF16 && out_dtype == PRB_BF16) DIFFT(__nv_bfloat16, __nv_bfloat16);
     else return PRB_E_DTYPE;
 #undef DIFFT
+    PRB_LAUNCH_CHECK();
+    return 0;
+}
+
+// Warps of the single-token kernel for these sizes (0: it does not take them).
+PRB_API int prb_diff_attention_single_warps(int heads, int kv_heads, int dim, int vdim) {
+    if (heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0) return 0;
+    const int hg = heads / kv_heads;
+    if (hg > DT_PPW || vdim > 32 * DT_VC || dim > 256) return 0;
+    const size_t fixed = (size_t)hg * 2 * dim * sizeof(float);
+    const size_t per_warp = (size_t)DT_KB * (2 * dim + 1 + vdim) * sizeof(float);
+    int nw = (int)((180 * 1024 - fixed) / per_warp);
+    if (nw > DT_WARPS) nw = DT_WARPS;
+    if (nw < hg) return 0;                           // (the join gives a pair to a warp)
+    return nw;
+}
+
+PRB_API int prb_diff_attention_single(void* out, long out_ld, const float* q, const void* cache,
+                                      const int* block_table, const int* seq_of_token,
+                                      const int* positions, int n_tokens, int heads, int kv_heads,
+                                      int dim, int vdim, int page_size, int max_pages,
+                                      int num_pages, int block, float scale, float lambda,
+                                      float eps, float out_scale, int cache_dtype, int out_dtype,
+                                      int* status, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    const int nw = prb_diff_attention_single_warps(heads, kv_heads, dim, vdim);
+    if (nw <= 0 || kv_heads > 65535 || page_size <= 0 || max_pages <= 0 || block < 0) return PRB_E_SIZE;
+    const int hg = heads / kv_heads;
+    size_t smem = (size_t)(nw * DT_KB * (2 * dim + 1 + vdim) + hg * 2 * dim) * sizeof(float);
+    const size_t join = (size_t)nw * hg * (4 + 2 * vdim) * sizeof(float);
+    if (join > smem) smem = join;
+    dim3 grid(n_tokens, kv_heads);
+#define DIFFS(CT, OT)                                                                            \
+    do {                                                                                         \
+        if (smem > 48 * 1024)                                                                    \
+            cudaFuncSetAttribute(diff_attention_single_kernel<CT, OT>,                           \
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);        \
+        diff_attention_single_kernel<CT, OT><<<grid, nw * 32, smem, stream>>>(                   \
+            (OT*)out, out_ld, q, (const CT*)cache, block_table, seq_of_token, positions,         \
+            n_tokens, heads, kv_heads, dim, vdim, page_size, max_pages, num_pages, block, scale, \
+            lambda, eps, out_scale, status);                                                     \
+    } while (0)
+    if (cache_dtype == PRB_F32 && out_dtype == PRB_F32) DIFFS(float, float);
+    else if (cache_dtype == PRB_BF16 && out_dtype == PRB_BF16) DIFFS(__nv_bfloat16, __nv_bfloat16);
+    else return PRB_E_DTYPE;
+#undef DIFFS
     PRB_LAUNCH_CHECK();
     return 0;
 }

@@ -161,6 +161,11 @@ def _declare(h: ctypes.CDLL) -> None:
     h.prb_diff_attention_tile.argtypes = [P, L, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, F,
                                           F, F, I, I, P, P]
     h.prb_diff_attention_tile.restype = c_int
+    h.prb_diff_attention_single_warps.argtypes = [I, I, I, I]
+    h.prb_diff_attention_single_warps.restype = c_int
+    h.prb_diff_attention_single.argtypes = [P, L, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, F, F,
+                                            F, I, I, P, P]
+    h.prb_diff_attention_single.restype = c_int
     for name in ("prb_embed_scaled", "prb_route_scores", "prb_routed_act", "prb_retention_lanes",
                  "prb_retention_scan", "prb_retention_finish", "prb_diff_prepare",
                  "prb_diff_attention"):
@@ -1284,14 +1289,22 @@ def diff_attention_tile_rows(heads: int, kv_heads: int, dim: int, vdim: int) -> 
     return int(lib().prb_diff_attention_tile_rows(heads, kv_heads, dim, vdim))
 
 
+def diff_attention_single_warps(heads: int, kv_heads: int, dim: int, vdim: int) -> int:
+    """Warps of the single-token kernel at these sizes; 0: it does not take them (more than
+    four query heads a key head, value heads wider than 128)."""
+    return int(lib().prb_diff_attention_single_warps(heads, kv_heads, dim, vdim))
+
+
 def diff_attention(out, q, cache, block_table, seq_of_token, positions, heads: int, dim: int,
                    vdim: int, block: int, scale: float, lam: float, eps: float, out_scale: float,
-                   status=None, tile_rows: int = 0) -> None:
+                   status=None, tile_rows: int = 0, single: bool = False) -> None:
     """Per (token, head): a1 - lam * a2 of two softmax attentions over the same values, then
     unit RMS over vdim times ``out_scale``.  A query at position p sees keys floor(p / block) *
     block .. p (``block`` 0: from 0).  32-bit arithmetic; out in the cache's type.
     ``tile_rows`` > 0: the tiled kernel, a CTA per (that many consecutive token rows, key/value
-    head), keys staged in shared memory once for all of them; 0: a CTA per (token, head)."""
+    head), keys staged in shared memory once for all of them; 0: a CTA per (token, head).
+    ``single``: the kernel for steps of single tokens, a CTA per (token, key/value head) whose
+    warps share the keys."""
     what = "diff_attention"
     _need(q, torch.float32, "q", what)
     _need(cache, None, "cache", what)
@@ -1303,6 +1316,13 @@ def diff_attention(out, q, cache, block_table, seq_of_token, positions, heads: i
     if rowlen != 2 * dim + vdim or q.shape[1] != heads * 2 * dim or out.dtype != cache.dtype or \
             out.stride(1) != 1 or out.shape[0] < n or out.shape[1] < heads * vdim:
         raise KernelArgumentError(f"{what}: shapes or types do not fit")
+    if single:
+        _check(lib().prb_diff_attention_single(
+            _p(out), out.stride(0), _p(q), _p(cache), _p(block_table), _p(seq_of_token),
+            _p(positions), n, heads, kv_heads, dim, vdim, page_size, block_table.shape[1], pages,
+            int(block or 0), float(scale), float(lam), float(eps), float(out_scale),
+            dtype_code(cache.dtype), dtype_code(out.dtype), _p(status), _stream()), what)
+        return
     if tile_rows > 0:
         _check(lib().prb_diff_attention_tile(
             _p(out), out.stride(0), _p(q), _p(cache), _p(block_table), _p(seq_of_token),

@@ -75,6 +75,8 @@ class DifferentialAttention(Mixer):
         # rows a CTA of the tiled kernel takes (0: the kernel of a CTA per (token, head))
         self.tile_rows = ops.diff_attention_tile_rows(self.heads, self.kv_heads, self.dim, self.vdim) \
             if torch.cuda.is_available() else 0
+        self.single_warps = ops.diff_attention_single_warps(self.heads, self.kv_heads, self.dim,
+                                                            self.vdim) if torch.cuda.is_available() else 0
 
     def kv_spec(self) -> KVSpec:
         return KVSpec(self.kv_heads, 2 * self.dim + self.vdim, None, values=False)
@@ -96,13 +98,15 @@ class DifferentialAttention(Mixer):
                          group.slots if cache.writes else None, ctx.positions, self.freq,
                          self.heads, self.kv_heads, self.dim, self.vdim, self.rot_dims, ctx.status)
         o = ctx.scratch_zero("diff_out", (cap, self.out.n_in), self.runtime.dtype)[:t]
-        # a step of single tokens: a CTA per (token, key/value head); portions of prompts: as
-        # many consecutive rows as the kernel takes, which share every key they stage
+        # a step of single tokens: a CTA per (token, key/value head) whose warps share the keys;
+        # portions of prompts: as many consecutive rows as the tiled kernel takes, which share
+        # every key they stage
         single = ctx.layout.t_cap <= ctx.layout.b_cap
         ops.diff_attention(o, q, cache.k, group.block_table, ctx.seq_of_token, ctx.positions,
                            self.heads, self.dim, self.vdim, self.block, self.scale, self.lam,
                            self.eps, self.out_scale, ctx.status,
-                           tile_rows=min(self.tile_rows, 1) if single else self.tile_rows)
+                           tile_rows=min(self.tile_rows, 1) if single else self.tile_rows,
+                           single=single and self.single_warps > 0)
         self.out.forward(ctx, o, x, resid=x if accumulate else None)
 
 

@@ -343,7 +343,8 @@ class DiffCase:
 
     def run(self, queries, heads, block, scale, lam, eps, factor, tile_rows=0):
         """queries: (request, position, q [heads, 2, dim]); returns kernel and plain results.
-        ``tile_rows``: 0 the kernel of a CTA per (token, head), else the tiled kernel."""
+        ``tile_rows``: 0 the kernel of a CTA per (token, head), -1 the single-token kernel, else
+        the tiled kernel."""
         from pretrained_rstr_b200.csrc import ops
         n = len(queries)
         q = torch.stack([x for _, _, x in queries]).reshape(n, -1).to(DEV).contiguous()
@@ -351,7 +352,8 @@ class DiffCase:
         status = torch.zeros(4, dtype=torch.int32, device=DEV)
         ops.diff_attention(out, q, self.cache, self.table, _i32([b for b, _, _ in queries]),
                            _i32([p for _, p, _ in queries]), heads, self.dim, self.vdim, block,
-                           scale, lam, eps, factor, status, tile_rows=tile_rows)
+                           scale, lam, eps, factor, status, tile_rows=max(tile_rows, 0),
+                           single=tile_rows < 0)
         assert int(status[0]) == 0, status.tolist()
         want = []
         for b, p, x in queries:
@@ -367,7 +369,7 @@ class DiffCase:
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("block", [0, 20, 64, 300])
-@pytest.mark.parametrize("tile_rows", [0, 1, 5, 10])
+@pytest.mark.parametrize("tile_rows", [-1, 0, 1, 5, 10])
 def test_differential_attention_kernel(dtype, block, tile_rows):
     """Random rows; queries at the first tokens, at page borders and on both sides of every
     block border; blocks shorter and longer than a page and than the kernel's key segment; a
@@ -386,7 +388,7 @@ def test_differential_attention_kernel(dtype, block, tile_rows):
     assert torch.allclose(got, want, atol=tol, rtol=tol)
 
 
-@pytest.mark.parametrize("tile_rows", [0, 4])
+@pytest.mark.parametrize("tile_rows", [-1, 0, 4])
 @pytest.mark.parametrize("block", [0, 50, 300])
 def test_differential_attention_edges_stand_out(block, tile_rows):
     """A key made to dominate map 1 at the first position of a block, and one at the last
