@@ -151,7 +151,11 @@ def _declare(h: ctypes.CDLL) -> None:
     h.prb_routed_act.argtypes = [P, L, P, L, I, I, I, P, L, I, I, I, I, P]
     h.prb_retention_lanes.argtypes = [I]
     h.prb_retention_scan.argtypes = [P, P, L, I, I, I, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I,
-                                     P, P]
+                                     P, P, I, P, P]
+    h.prb_retention_segment.argtypes = []
+    h.prb_retention_segment.restype = c_int
+    h.prb_retention_max_segments.argtypes = [I, I]
+    h.prb_retention_max_segments.restype = c_int
     h.prb_retention_finish.argtypes = [P, L, P, P, L, I, P, I, I, I, F, I, P]
     h.prb_diff_prepare.argtypes = [P, P, P, L, I, I, I, P, P, P, I, I, I, I, I, I, I, I, I, P, P]
     h.prb_diff_attention.argtypes = [P, L, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, F, F, F, I,
@@ -1201,15 +1205,28 @@ def retention_lanes(dim: int) -> int:
     return int(lib().prb_retention_lanes(int(dim)))
 
 
+def retention_segment() -> int:
+    """Tokens of a segment of the segmented scan."""
+    return int(lib().prb_retention_segment())
+
+
+def retention_max_segments(t_cap: int, b_cap: int) -> int:
+    """Most segments a step of ``t_cap`` token rows and ``b_cap`` requests can have."""
+    return int(lib().prb_retention_max_segments(int(t_cap), int(b_cap)))
+
+
 def retention_scan(o_raw, proj, q_col: int, k_col: int, v_col: int, state, q_start, state_slot,
                    positions, decay, freq, n_requests: int, heads: int, dim: int, vdim: int,
-                   rot_dims: int, k_scale: float, cols: int, status=None) -> None:
+                   rot_dims: int, k_scale: float, cols: int, status=None, segments=None) -> None:
     """o_raw[t, h] = S_t^T q_t with S_t = decay_h S_(t-1) + k_t v_t^T per request and head, over
     the step's tokens in order, from and back to ``state`` [slots, heads, vdim, dim] float32
     (zero at position 0).  proj float32 [T, ld] holds q, k (heads * dim) and v (heads * vdim)
     at the given columns; q and k are first rotated IN PLACE in ``proj`` (rotate-half, the first
     ``rot_dims`` coordinates; one launch for all tokens) and k scaled by ``k_scale``.  ``cols``:
-    value columns per CTA."""
+    value columns per CTA.  ``segments`` = (own, start): two float32 workspaces [n, heads, vdim,
+    dim] with n >= retention_max_segments(rows of o_raw, n_requests): portions are cut into
+    segments of retention_segment() tokens that run side by side (every segment's own sum, the
+    states at the segments' starts one after the other, then the segments with outputs)."""
     what = "retention_scan"
     _need(o_raw, torch.float32, "o_raw", what)
     _need(state, torch.float32, "state", what)
@@ -1225,13 +1242,23 @@ def retention_scan(o_raw, proj, q_col: int, k_col: int, v_col: int, state, q_sta
             state_slot.numel() < n_requests or freq.numel() < max(1, rot_dims // 2) or \
             max(q_col, k_col) + heads * dim > proj.shape[1] or v_col + heads * vdim > proj.shape[1]:
         raise KernelArgumentError(f"{what}: shapes do not fit")
+    seg_own = seg_start = None
+    n_seg = 0
+    if segments is not None:
+        seg_own, seg_start = segments
+        for name, t in (("segments[0]", seg_own), ("segments[1]", seg_start)):
+            _need(t, torch.float32, name, what)
+            if tuple(t.shape[1:]) != (heads, vdim, dim):
+                raise KernelArgumentError(f"{what}: {name} must be [n, heads, vdim, dim]")
+        n_seg = min(seg_own.shape[0], seg_start.shape[0])
     _check(lib().prb_retention_scan(_p(o_raw), _p(proj), proj.stride(0), int(q_col), int(k_col),
                                     int(v_col), _p(state), _p(q_start), _p(state_slot),
                                     _p(positions), _p(decay), _p(freq), n, int(n_requests),
                                     state.shape[0], heads, dim, vdim, int(rot_dims), float(k_scale),
-                                    int(cols), _p(status), _stream()), what)
-    if rot_dims > 0 or float(k_scale) != 1.0:
-        add_launches(1)                                # (the rotation is a launch of its own)
+                                    int(cols), _p(seg_own), _p(seg_start), n_seg, _p(status),
+                                    _stream()), what)
+    # (the rotation is a launch of its own; the segmented scan is three)
+    add_launches((1 if rot_dims > 0 or float(k_scale) != 1.0 else 0) + (2 if n_seg else 0))
 
 
 def retention_finish(out, o_raw, proj, g_col: int, seq_of_token, heads: int, vdim: int,

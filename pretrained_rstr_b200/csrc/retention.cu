@@ -34,6 +34,9 @@ struct ScanArgs {
     const float* decay;       // [heads]
     int n_tokens, n_slots, heads, dim, vdim, cols, lanes;   // lanes = R
     int* status;
+    int n_requests, seg_len;  // segments (see below); seg_len 0: none
+    float* seg_own;           // [segments, heads, vdim, dim]: pass 1's sums
+    float* seg_start;         // [segments, heads, vdim, dim]: the states at the segments' starts
 };
 
 // q and k of every token of the step, in place in the projection's 32-bit result: the first
@@ -69,13 +72,45 @@ __global__ void retention_rotate_kernel(float* __restrict__ proj, long ld, int q
     }
 }
 
-template <int RET_NI>
+// Long portions are cut into segments of `seg_len` tokens that run side by side:
+//   pass 1 (MODE 1): every segment but a request's last builds, from zero, what its own tokens
+//           add to the state (no queries, no outputs);
+//   pass 2 (carry):  per request the states at the segments' starts, one after the other:
+//           U_0 = the carried state, U_(s+1) = decay^seg_len U_s + (pass 1 of segment s);
+//   pass 3 (MODE 2): every segment runs the recurrence from its U_s with outputs; a request's
+//           last segment leaves the state in the request's slot.
+// MODE 0 is the whole portion by one CTA from and to the slot (steps of few tokens).
+// Segment z of the launch is segment s of request b: requests' segments are numbered in
+// request order (a CTA finds its own by walking q_start).
+__device__ __forceinline__ bool find_segment(const int* q_start, int n_requests, int seg_len, int z,
+                                             int& b, int& s, int& nseg) {
+    int base = 0;
+    for (b = 0; b < n_requests; ++b) {
+        const int n = q_start[b + 1] - q_start[b];
+        nseg = n > 0 ? (n + seg_len - 1) / seg_len : 0;
+        if (z < base + nseg) {
+            s = z - base;
+            return true;
+        }
+        base += nseg;
+    }
+    return false;
+}
+
+template <int RET_NI, int MODE>
 __global__ void retention_scan_kernel(ScanArgs a) {
     extern __shared__ __align__(16) float smem[];
     prb_grid_launch_dependents();
-    const int chunk = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
-    const int t0 = a.q_start[b], t1 = a.q_start[b + 1];
+    const int chunk = blockIdx.x, h = blockIdx.y;
+    int b = blockIdx.z, s = 0, nseg = 1;
+    if (MODE != 0 && !find_segment(a.q_start, a.n_requests, a.seg_len, blockIdx.z, b, s, nseg)) return;
+    int t0 = a.q_start[b], t1 = a.q_start[b + 1];
     if (t1 <= t0 || t0 < 0 || t1 > a.n_tokens) return;
+    if (MODE != 0) {
+        if (MODE == 1 && s == nseg - 1) return;      // (a last segment's own sum is never needed)
+        t0 += s * a.seg_len;
+        t1 = min(t1, t0 + a.seg_len);
+    }
     const int R = a.lanes, dim_pad = R * RET_NI;
     float* qs = smem;                               // [RET_BLOCK][dim_pad]
     float* ks = qs + RET_BLOCK * dim_pad;           // [RET_BLOCK][dim_pad]
@@ -88,13 +123,20 @@ __global__ void retention_scan_kernel(ScanArgs a) {
         if (threadIdx.x == 0) prb_set_status(a.status, PRB_S_SLOT_RANGE, t0, slot, a.n_slots);
         return;
     }
-    const int pos0 = a.positions[t0];
-    float* srow = a.state + (((size_t)slot * a.heads + h) * a.vdim + (live ? col : 0)) * a.dim;
+    const size_t column = ((size_t)h * a.vdim + (live ? col : 0)) * a.dim;
+    const size_t per_state = (size_t)a.heads * a.vdim * a.dim;
+    float* srow = a.state + (size_t)slot * per_state + column;
     float S[RET_NI];
+    {
+        // where the state comes from: the slot (zero at position 0), zero, or pass 2's U
+        const float* from = nullptr;
+        if (MODE == 0 && a.positions[t0] > 0) from = srow;
+        if (MODE == 2) from = a.seg_start + (size_t)blockIdx.z * per_state + column;
 #pragma unroll
-    for (int ii = 0; ii < RET_NI; ++ii) {
-        const int i = r * RET_NI + ii;
-        S[ii] = (live && pos0 > 0 && i < a.dim) ? srow[i] : 0.0f;
+        for (int ii = 0; ii < RET_NI; ++ii) {
+            const int i = r * RET_NI + ii;
+            S[ii] = (live && from != nullptr && i < a.dim) ? from[i] : 0.0f;
+        }
     }
     const float decay = a.decay[h];
     for (int tb = t0; tb < t1; tb += RET_BLOCK) {
@@ -103,7 +145,7 @@ __global__ void retention_scan_kernel(ScanArgs a) {
         for (int u = threadIdx.x; u < nb * a.dim; u += blockDim.x) {
             const int tok = u / a.dim, i = u - tok * a.dim;
             const float* row = a.proj + (size_t)(tb + tok) * a.ld + h * a.dim + i;
-            qs[tok * dim_pad + i] = row[a.q_col];
+            if (MODE != 1) qs[tok * dim_pad + i] = row[a.q_col];
             ks[tok * dim_pad + i] = row[a.k_col];
         }
         for (int u = threadIdx.x; u < nb * (dim_pad - a.dim); u += blockDim.x) {
@@ -126,27 +168,68 @@ __global__ void retention_scan_kernel(ScanArgs a) {
             float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
             for (int g = 0; g < RET_NI / 4; ++g) {      // (sums in an order that dim alone fixes)
-                const float4 kk = k4[g], qq = q4[g];
+                const float4 kk = k4[g];
                 S[4 * g + 0] = fmaf(decay, S[4 * g + 0], kk.x * v);
                 S[4 * g + 1] = fmaf(decay, S[4 * g + 1], kk.y * v);
                 S[4 * g + 2] = fmaf(decay, S[4 * g + 2], kk.z * v);
                 S[4 * g + 3] = fmaf(decay, S[4 * g + 3], kk.w * v);
-                acc[0] = fmaf(S[4 * g + 0], qq.x, acc[0]);
-                acc[1] = fmaf(S[4 * g + 1], qq.y, acc[1]);
-                acc[2] = fmaf(S[4 * g + 2], qq.z, acc[2]);
-                acc[3] = fmaf(S[4 * g + 3], qq.w, acc[3]);
+                if (MODE != 1) {
+                    const float4 qq = q4[g];
+                    acc[0] = fmaf(S[4 * g + 0], qq.x, acc[0]);
+                    acc[1] = fmaf(S[4 * g + 1], qq.y, acc[1]);
+                    acc[2] = fmaf(S[4 * g + 2], qq.z, acc[2]);
+                    acc[3] = fmaf(S[4 * g + 3], qq.w, acc[3]);
+                }
             }
-            float o = (acc[0] + acc[1]) + (acc[2] + acc[3]);
-            for (int m = 1; m < R; m <<= 1) o += __shfl_xor_sync(0xffffffffu, o, m);
-            if (live && r == 0)
-                a.o_raw[(size_t)(tb + tok) * a.heads * a.vdim + h * a.vdim + col] = o;
+            if (MODE != 1) {
+                float o = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+                for (int m = 1; m < R; m <<= 1) o += __shfl_xor_sync(0xffffffffu, o, m);
+                if (live && r == 0)
+                    a.o_raw[(size_t)(tb + tok) * a.heads * a.vdim + h * a.vdim + col] = o;
+            }
         }
     }
-    if (live) {
+    // where the state goes: the slot, pass 1's own sums, or (a last segment) the slot
+    float* to = nullptr;
+    if (MODE == 0 || (MODE == 2 && s == nseg - 1)) to = srow;
+    if (MODE == 1) to = a.seg_own + (size_t)blockIdx.z * per_state + column;
+    if (live && to != nullptr) {
 #pragma unroll
         for (int ii = 0; ii < RET_NI; ++ii) {
             const int i = r * RET_NI + ii;
-            if (i < a.dim) srow[i] = S[ii];
+            if (i < a.dim) to[i] = S[ii];
+        }
+    }
+}
+
+// Pass 2: a thread per state number of a (head, request), 1,024 numbers a CTA; the request's
+// segments in order.
+__global__ void retention_carry_kernel(ScanArgs a) {
+    prb_grid_launch_dependents();
+    const int h = blockIdx.x, b = blockIdx.y;
+    const int t0 = a.q_start[b], t1 = a.q_start[b + 1];
+    if (t1 <= t0 || t0 < 0 || t1 > a.n_tokens) return;
+    const int slot = a.state_slot[b];
+    if (slot < 0 || slot >= a.n_slots) return;
+    int base = 0;
+    for (int bb = 0; bb < b; ++bb) {
+        const int n = a.q_start[bb + 1] - a.q_start[bb];
+        base += n > 0 ? (n + a.seg_len - 1) / a.seg_len : 0;
+    }
+    const int nseg = (t1 - t0 + a.seg_len - 1) / a.seg_len;
+    const size_t per_state = (size_t)a.heads * a.vdim * a.dim;
+    const size_t per_head = (size_t)a.vdim * a.dim;
+    const bool carried = a.positions[t0] > 0;
+    const float decay = a.decay[h];
+    float step = 1.0f;                              // decay^seg_len, by multiplication in 32-bit
+    for (int i = 0; i < a.seg_len; ++i) step *= decay;
+    for (size_t e = (size_t)blockIdx.z * 1024 + threadIdx.x;
+         e < min(per_head, ((size_t)blockIdx.z + 1) * 1024); e += blockDim.x) {
+        const size_t at = (size_t)h * per_head + e;
+        float S = carried ? a.state[(size_t)slot * per_state + at] : 0.0f;
+        for (int s = 0; s < nseg; ++s) {
+            a.seg_start[(size_t)(base + s) * per_state + at] = S;
+            if (s + 1 < nseg) S = fmaf(step, S, a.seg_own[(size_t)(base + s) * per_state + at]);
         }
     }
 }
@@ -194,19 +277,44 @@ PRB_API int prb_retention_lanes(int dim) {
     return r <= 32 ? r : 0;
 }
 
-// Rotates q and k IN PLACE in `proj` (and scales k), then runs the scan.
+// Tokens of a segment, and the most segments a step of `t_cap` token rows and `b_cap` requests
+// can have (what the two workspaces are sized for).
+PRB_API int prb_retention_segment() { return 64; }
+PRB_API int prb_retention_max_segments(int t_cap, int b_cap) {
+    return t_cap / prb_retention_segment() + b_cap;
+}
+
+template <int NI>
+static void launch_scan(const ScanArgs& a, int mode, dim3 grid, int threads, size_t smem,
+                        cudaStream_t stream) {
+    if (smem > 48 * 1024) {
+        cudaFuncSetAttribute(retention_scan_kernel<NI, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaFuncSetAttribute(retention_scan_kernel<NI, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaFuncSetAttribute(retention_scan_kernel<NI, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    }
+    if (mode == 0) retention_scan_kernel<NI, 0><<<grid, threads, smem, stream>>>(a);
+    else if (mode == 1) retention_scan_kernel<NI, 1><<<grid, threads, smem, stream>>>(a);
+    else retention_scan_kernel<NI, 2><<<grid, threads, smem, stream>>>(a);
+}
+
+// Rotates q and k IN PLACE in `proj` (and scales k), then runs the scan: by one CTA per
+// (columns, head, request), or, with workspaces (`seg_own`, `seg_start`: room for `segments`
+// states each), in segments side by side (three launches).
 PRB_API int prb_retention_scan(float* o_raw, float* proj, long ld, int q_col, int k_col,
                                int v_col, float* state, const int* q_start, const int* state_slot,
                                const int* positions, const float* decay, const float* freq,
                                int n_tokens, int n_requests, int n_slots, int heads, int dim,
-                               int vdim, int rot_dims, float k_scale, int cols, int* status,
-                               cudaStream_t stream) {
+                               int vdim, int rot_dims, float k_scale, int cols, float* seg_own,
+                               float* seg_start, int segments, int* status, cudaStream_t stream) {
     if (n_tokens <= 0 || n_requests <= 0) return 0;
     const int lanes = prb_retention_lanes(dim);
     if (heads <= 0 || heads > 65535 || n_requests > 65535 || dim <= 0 || vdim <= 0 || lanes == 0 ||
         rot_dims < 0 || rot_dims > dim || rot_dims % 2 != 0 || cols <= 0)
         return PRB_E_SIZE;
     if (ld % 4 != 0 || ((uintptr_t)proj) % 16 != 0) return PRB_E_ALIGN;
+    const bool segmented = seg_own != nullptr && seg_start != nullptr && segments > 0;
+    if (segmented && (segments > 65535 || segments < prb_retention_max_segments(n_tokens, n_requests)))
+        return PRB_E_SIZE;
     if (rot_dims > 0 || k_scale != 1.0f) {
         const int work = heads * (dim - rot_dims / 2);
         const int rt = work >= 256 ? 256 : ((work + 31) / 32) * 32;
@@ -221,17 +329,24 @@ PRB_API int prb_retention_scan(float* o_raw, float* proj, long ld, int q_col, in
     const int chunks = (vdim + cols - 1) / cols;
     const int ni = ret_ni(dim);
     ScanArgs a{o_raw, proj, ld, q_col, k_col, v_col, state, q_start, state_slot, positions, decay,
-               n_tokens, n_slots, heads, dim, vdim, cols, lanes, status};
+               n_tokens, n_slots, heads, dim, vdim, cols, lanes, status, n_requests,
+               segmented ? prb_retention_segment() : 0, seg_own, seg_start};
     const size_t smem = (size_t)RET_BLOCK * (2 * lanes * ni + cols) * sizeof(float);
-    const dim3 grid(chunks, heads, n_requests);
-    if (ni == 4) {
-        retention_scan_kernel<4><<<grid, threads, smem, stream>>>(a);
-    } else {
-        if (smem > 48 * 1024)
-            cudaFuncSetAttribute(retention_scan_kernel<16>,
-                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        retention_scan_kernel<16><<<grid, threads, smem, stream>>>(a);
+    if (!segmented) {
+        const dim3 grid(chunks, heads, n_requests);
+        if (ni == 4) launch_scan<4>(a, 0, grid, threads, smem, stream);
+        else launch_scan<16>(a, 0, grid, threads, smem, stream);
+        PRB_LAUNCH_CHECK();
+        return 0;
     }
+    const dim3 grid(chunks, heads, prb_retention_max_segments(n_tokens, n_requests));
+    if (ni == 4) launch_scan<4>(a, 1, grid, threads, smem, stream);
+    else launch_scan<16>(a, 1, grid, threads, smem, stream);
+    PRB_LAUNCH_CHECK();
+    retention_carry_kernel<<<dim3(heads, n_requests, ((size_t)vdim * dim + 1023) / 1024), 256, 0, stream>>>(a);
+    PRB_LAUNCH_CHECK();
+    if (ni == 4) launch_scan<4>(a, 2, grid, threads, smem, stream);
+    else launch_scan<16>(a, 2, grid, threads, smem, stream);
     PRB_LAUNCH_CHECK();
     return 0;
 }

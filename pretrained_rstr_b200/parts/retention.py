@@ -9,7 +9,8 @@ first ``rot_dims`` coordinates of q and k, k scaled by ``k_scale`` after the rot
 then each head's o is brought to unit root-mean-square, the heads are gated by silu(G h)
 (``gate``: optional) and projected.  The state [heads, vdim, dim] is 32-bit, starts at zero
 and is per-request STATE of the cache manager (a slot per live request), so a prompt may be
-cut anywhere and decoding is the same kernel with one token.  Projections Q, K, V and G are
+cut anywhere and decoding is the same kernel with one token; long portions are cut into
+segments that run side by side, joined by the states at their starts.  Projections Q, K, V and G are
 one matrix product whose 32-bit result feeds the recurrence unrounded.  Sizes, decays, the
 rotation's base and reach, the key scale and eps are parameters.
 """
@@ -88,10 +89,21 @@ class Retention(Mixer):
         cols = self.input.cols
         raw = ctx.scratch("retention_raw", (cap, self.heads * self.vdim), torch.float32)[:t]
         requests = ctx.layout.b_cap
+        # a step with room for more tokens than a segment: portions are cut into segments that
+        # run side by side (workspaces sized once, for the largest step the runtime takes)
+        segments = None
+        if ctx.layout.t_cap > ops.retention_segment():
+            n = ops.retention_max_segments(max(ctx.runtime.max_batched_tokens, ctx.layout.t_cap),
+                                           max(ctx.runtime.max_requests, requests))
+            shape = (n, self.heads, self.vdim, self.dim)
+            segments = (ctx.scratch("retention_seg_own", shape, torch.float32),
+                        ctx.scratch("retention_seg_start", shape, torch.float32))
+        lists = n if segments else requests
         ops.retention_scan(raw, proj, cols["q"][0], cols["k"][0], cols["v"][0],
                            cache.state["retention"], ctx.q_start, ctx.state_slot, ctx.positions,
                            self.decay, self.freq, requests, self.heads, self.dim, self.vdim,
-                           self.rot_dims, self.k_scale, self._columns_per_cta(requests), ctx.status)
+                           self.rot_dims, self.k_scale, self._columns_per_cta(lists), ctx.status,
+                           segments=segments)
         gated = ctx.scratch_zero("retention_gated", (cap, self.out.n_in), self.runtime.dtype)[:t]
         ops.retention_finish(gated, raw, proj if self.gated else None,
                              cols["gate"][0] if self.gated else 0, ctx.seq_of_token, self.heads,

@@ -232,8 +232,9 @@ class RetentionCase:
         gd = gate.double()
         return P.unit_rms(o, eps) * gd * torch.sigmoid(gd)
 
-    def run(self, parts, eps, cols, out_dtype=torch.float32):
-        """parts: (slot, first position, q, k, v, gate) per request of one step."""
+    def run(self, parts, eps, cols, out_dtype=torch.float32, segmented=False):
+        """parts: (slot, first position, q, k, v, gate) per request of one step; ``segmented``:
+        portions cut into segments that run side by side."""
         from pretrained_rstr_b200.csrc import ops
         from pretrained_rstr_b200.parts.positions_rotary import rotary_frequencies
         h, d, vd = self.heads, self.dim, self.vdim
@@ -253,9 +254,13 @@ class RetentionCase:
         status = torch.zeros(4, dtype=torch.int32, device=DEV)
         decay = torch.tensor(self.decay, dtype=torch.float32, device=DEV)
         freq = rotary_frequencies(self.base, self.rot_dims, DEV)
+        segments = None
+        if segmented:
+            n = ops.retention_max_segments(t, len(parts) + 1)
+            segments = (torch.full((n, h, vd, d), 7.0, device=DEV), torch.full((n + 2, h, vd, d), 7.0, device=DEV))
         ops.retention_scan(raw, proj, 4, 4 + h * d, 8 + 2 * h * d, self.state, _i32(qs + [qs[-1]]),
                            _i32(slots + [0]), _i32(pos), decay, freq, len(parts) + 1, h, d, vd,
-                           self.rot_dims, self.k_scale, cols, status)
+                           self.rot_dims, self.k_scale, cols, status, segments=segments)
         assert int(status[0]) == 0
         out = torch.zeros(t, h * vd + 8, dtype=out_dtype, device=DEV)
         ops.retention_finish(out, raw, proj, 8 + 2 * h * d + h * vd, _i32(seq), h, vd, eps)
@@ -275,6 +280,19 @@ def test_retention_kernels(heads, dim, vdim, rot_dims):
     want, want2 = case.plain(q, k, v, gate, 1e-5), case.plain(q2, k2, v2, gate2, 1e-5)
     got = case.run([(1, 0, q, k, v, gate)], 1e-5, cols=vdim)
     assert torch.allclose(got, want, atol=2e-5, rtol=2e-5)
+    # segments side by side: a portion of one full segment and a rest, one of exactly two, a
+    # short one, and a continuation from a carried state
+    q3, k3, v3, gate3 = case.rows(128)
+    want3 = case.plain(q3, k3, v3, gate3, 1e-5)
+    got = case.run([(1, 0, q[:70], k[:70], v[:70], gate[:70]), (2, 0, q3, k3, v3, gate3),
+                    (0, 0, q2[:5], k2[:5], v2[:5], gate2[:5])], 1e-5, cols=7, segmented=True)
+    assert torch.allclose(got[:70], want[:70], atol=2e-5, rtol=2e-5)
+    assert torch.allclose(got[70:198], want3, atol=2e-5, rtol=2e-5)
+    assert torch.allclose(got[198:], want2[:5], atol=2e-5, rtol=2e-5)
+    got = case.run([(0, 5, q2[5:], k2[5:], v2[5:], gate2[5:]), (1, 70, q[70:], k[70:], v[70:], gate[70:])],
+                   1e-5, cols=vdim, segmented=True)
+    assert torch.allclose(got[:32], want2[5:], atol=2e-5, rtol=2e-5)
+    assert torch.allclose(got[32:], want[70:], atol=2e-5, rtol=2e-5)
     at, outs = 0, []
     for size in (1, 2, 17, 1, 33, 16, 20):
         # a portion of the request; beside it, before or after, a fresh request in another slot
@@ -307,7 +325,7 @@ def test_retention_far_token_stands_out():
     outs, at = [], 0
     for size in [130, 64, 2, 190] + [1] * 14:
         outs.append(case.run([(0, at, q[at:at + size], k[at:at + size], v[at:at + size],
-                               gate[at:at + size])], 1e-6, cols=16))
+                               gate[at:at + size])], 1e-6, cols=16, segmented=size > 64))
         at += size
     got = torch.cat(outs)
     assert at == n and torch.allclose(got, want, atol=1e-4, rtol=1e-4)
