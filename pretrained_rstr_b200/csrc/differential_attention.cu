@@ -248,7 +248,7 @@ constexpr int DT_PPW = 4;            // (query, head) pairs a warp owns
 constexpr int DT_VC = 4;             // value coordinates a lane owns at most (vdim <= 128)
 constexpr int DT_KB = 32;            // keys per block
 
-template <typename C, typename O>
+template <typename C, typename O, int VC>
 __global__ void __launch_bounds__(DT_WARPS * 32)
 diff_attention_tile_kernel(O* __restrict__ out, long out_ld, const float* __restrict__ q,
                            const C* __restrict__ cache, const int* __restrict__ block_table,
@@ -302,14 +302,14 @@ diff_attention_tile_kernel(O* __restrict__ out, long out_ld, const float* __rest
             const int qi = pair / hg, hh = pair - qi * hg;
             Qs[pair * 2 * dim + d] = q[((size_t)(r + qi) * heads + g * hg + hh) * 2 * dim + d] * scale;
         }
-        float acc1[DT_PPW][DT_VC], acc2[DT_PPW][DT_VC];
+        float acc1[DT_PPW][VC], acc2[DT_PPW][VC];
         float m1[DT_PPW], m2[DT_PPW], l1[DT_PPW], l2[DT_PPW];
 #pragma unroll
         for (int x = 0; x < DT_PPW; ++x) {
             m1[x] = m2[x] = -INFINITY;
             l1[x] = l2[x] = 0.0f;
 #pragma unroll
-            for (int c = 0; c < DT_VC; ++c) acc1[x][c] = acc2[x][c] = 0.0f;
+            for (int c = 0; c < VC; ++c) acc1[x][c] = acc2[x][c] = 0.0f;
         }
         for (int j0 = (lo_min / DT_KB) * DT_KB; j0 <= p_last; j0 += DT_KB) {
             __syncthreads();                         // the block before has been consumed
@@ -356,48 +356,84 @@ diff_attention_tile_kernel(O* __restrict__ out, long out_ld, const float* __rest
                 }
             }
             __syncthreads();
+            // scores of this lane's key for all pairs of the warp: a key's numbers are loaded
+            // once for the pairs, a pair's query in 16-byte pieces
             const int j = j0 + lane;
             const float* krow = Ks + lane * kpitch;
+            bool act[DT_PPW];
+            int last[DT_PPW], first[DT_PPW];
+            float s1[DT_PPW], s2[DT_PPW];
+            int k_hi = 0;
 #pragma unroll
             for (int x = 0; x < DT_PPW; ++x) {
-                const int pair = x * DT_WARPS + warp;        // (few pairs spread over the warps)
-                if (pair >= n_pairs) break;
-                const int qi = pair / hg;
-                const int pi = p0 + qi;
-                const int lo = block > 0 ? (pi / block) * block : 0;
-                if (j0 > pi || j0 + DT_KB <= lo) continue;       // nothing of this block is seen
-                const bool vis = j >= lo && j <= pi;
-                const float* qrow = Qs + pair * 2 * dim;
-                float s1 = 0.0f, s2 = 0.0f;
-                for (int d = 0; d < dim; ++d) {
-                    s1 = fmaf(qrow[d], krow[d], s1);
-                    s2 = fmaf(qrow[dim + d], krow[dim + d], s2);
+                const int pair = x * DT_WARPS + warp;
+                const int pi = p0 + (pair < n_pairs ? pair / hg : 0);
+                first[x] = block > 0 ? (pi / block) * block : 0;
+                last[x] = pi;
+                act[x] = pair < n_pairs && j0 <= pi && j0 + DT_KB > first[x];
+                if (act[x]) k_hi = max(k_hi, min(DT_KB, pi - j0 + 1));
+                s1[x] = s2[x] = 0.0f;
+            }
+            if (k_hi == 0) continue;                     // nothing of this block is seen by the warp
+            if (dim % 4 == 0) {
+                for (int d = 0; d < dim; d += 4) {
+                    const float a0 = krow[d], a1 = krow[d + 1], a2 = krow[d + 2], a3 = krow[d + 3];
+                    const float b0 = krow[dim + d], b1 = krow[dim + d + 1], b2 = krow[dim + d + 2],
+                                b3 = krow[dim + d + 3];
+#pragma unroll
+                    for (int x = 0; x < DT_PPW; ++x) {
+                        const float* qrow = Qs + (x * DT_WARPS + warp) * 2 * dim;
+                        const float4 u = *reinterpret_cast<const float4*>(qrow + d);
+                        const float4 w = *reinterpret_cast<const float4*>(qrow + dim + d);
+                        s1[x] = fmaf(u.w, a3, fmaf(u.z, a2, fmaf(u.y, a1, fmaf(u.x, a0, s1[x]))));
+                        s2[x] = fmaf(w.w, b3, fmaf(w.z, b2, fmaf(w.y, b1, fmaf(w.x, b0, s2[x]))));
+                    }
                 }
-                s1 = vis ? s1 : -INFINITY;
-                s2 = vis ? s2 : -INFINITY;
-                const float n1 = fmaxf(m1[x], prb_warp_max(s1)), n2 = fmaxf(m2[x], prb_warp_max(s2));
+            } else {
+                for (int d = 0; d < dim; ++d) {
+                    const float a0 = krow[d], b0 = krow[dim + d];
+#pragma unroll
+                    for (int x = 0; x < DT_PPW; ++x) {
+                        const float* qrow = Qs + (x * DT_WARPS + warp) * 2 * dim;
+                        s1[x] = fmaf(qrow[d], a0, s1[x]);
+                        s2[x] = fmaf(qrow[dim + d], b0, s2[x]);
+                    }
+                }
+            }
+            float e1[DT_PPW], e2[DT_PPW];
+#pragma unroll
+            for (int x = 0; x < DT_PPW; ++x) {
+                e1[x] = e2[x] = 0.0f;
+                if (!act[x]) continue;
+                const bool vis = j >= first[x] && j <= last[x];
+                const float t1 = vis ? s1[x] : -INFINITY, t2 = vis ? s2[x] : -INFINITY;
+                const float n1 = fmaxf(m1[x], prb_warp_max(t1)), n2 = fmaxf(m2[x], prb_warp_max(t2));
                 const float f1 = expf(m1[x] - n1), f2 = expf(m2[x] - n2);    // (exp(-inf) = 0)
-                const float e1 = vis ? expf(s1 - n1) : 0.0f, e2 = vis ? expf(s2 - n2) : 0.0f;
-                l1[x] = l1[x] * f1 + prb_warp_sum(e1);
-                l2[x] = l2[x] * f2 + prb_warp_sum(e2);
+                e1[x] = vis ? expf(t1 - n1) : 0.0f;
+                e2[x] = vis ? expf(t2 - n2) : 0.0f;
+                l1[x] = l1[x] * f1 + prb_warp_sum(e1[x]);
+                l2[x] = l2[x] * f2 + prb_warp_sum(e2[x]);
                 m1[x] = n1;
                 m2[x] = n2;
 #pragma unroll
-                for (int c = 0; c < DT_VC; ++c) {
+                for (int c = 0; c < VC; ++c) {
                     acc1[x][c] *= f1;
                     acc2[x][c] *= f2;
                 }
-                const int k_hi = min(DT_KB, pi - j0 + 1);
-                for (int kk = 0; kk < k_hi; ++kk) {
-                    const float w1 = __shfl_sync(0xffffffffu, e1, kk), w2 = __shfl_sync(0xffffffffu, e2, kk);
+            }
+            // weighted values: a key's value coordinates are loaded once for the pairs (keys a
+            // pair does not see have weight zero)
+            for (int kk = 0; kk < k_hi; ++kk) {
+                float v[VC];
 #pragma unroll
-                    for (int c = 0; c < DT_VC; ++c) {
-                        const int col = lane + 32 * c;
-                        if (col < vdim) {
-                            const float v = Vs[kk * vdim + col];
-                            acc1[x][c] = fmaf(w1, v, acc1[x][c]);
-                            acc2[x][c] = fmaf(w2, v, acc2[x][c]);
-                        }
+                for (int c = 0; c < VC; ++c) v[c] = (lane + 32 * c < vdim) ? Vs[kk * vdim + lane + 32 * c] : 0.0f;
+#pragma unroll
+                for (int x = 0; x < DT_PPW; ++x) {
+                    const float w1 = __shfl_sync(0xffffffffu, e1[x], kk), w2 = __shfl_sync(0xffffffffu, e2[x], kk);
+#pragma unroll
+                    for (int c = 0; c < VC; ++c) {
+                        acc1[x][c] = fmaf(w1, v[c], acc1[x][c]);
+                        acc2[x][c] = fmaf(w2, v[c], acc2[x][c]);
                     }
                 }
             }
@@ -408,10 +444,10 @@ diff_attention_tile_kernel(O* __restrict__ out, long out_ld, const float* __rest
             const int pair = x * DT_WARPS + warp;        // (few pairs spread over the warps)
             if (pair >= n_pairs) break;
             const int qi = pair / hg, hh = pair - qi * hg;
-            float o[DT_VC];
+            float o[VC];
             float ss = 0.0f;
 #pragma unroll
-            for (int c = 0; c < DT_VC; ++c) {
+            for (int c = 0; c < VC; ++c) {
                 const float a1 = l1[x] > 0.0f ? acc1[x][c] / l1[x] : 0.0f;
                 const float a2 = l2[x] > 0.0f ? acc2[x][c] / l2[x] : 0.0f;
                 o[c] = (lane + 32 * c < vdim) ? a1 - lambda * a2 : 0.0f;
@@ -421,7 +457,7 @@ diff_attention_tile_kernel(O* __restrict__ out, long out_ld, const float* __rest
             const float inv = out_scale / sqrtf(ss / (float)vdim + eps);
             O* dst = out + (size_t)(r + qi) * out_ld + (size_t)(g * hg + hh) * vdim;
 #pragma unroll
-            for (int c = 0; c < DT_VC; ++c)
+            for (int c = 0; c < VC; ++c)
                 if (lane + 32 * c < vdim) dst[lane + 32 * c] = prb_from_float<O>(o[c] * inv);
         }
         r = r1 + 1;
@@ -700,20 +736,30 @@ PRB_API int prb_diff_attention_tile(void* out, long out_ld, const float* q, cons
     if (tq <= 0 || tq > most) tq = most;
     const size_t smem = (size_t)(DT_KB * (2 * dim + 1) + DT_KB * vdim + DT_WARPS * DT_PPW * 2 * dim) * sizeof(float);
     dim3 grid((n_tokens + tq - 1) / tq, kv_heads);
-#define DIFFT(CT, OT)                                                                            \
+#define DIFFT1(CT, OT, VCN)                                                                      \
     do {                                                                                         \
         if (smem > 48 * 1024)                                                                    \
-            cudaFuncSetAttribute(diff_attention_tile_kernel<CT, OT>,                             \
+            cudaFuncSetAttribute(diff_attention_tile_kernel<CT, OT, VCN>,                        \
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);        \
-        diff_attention_tile_kernel<CT, OT><<<grid, DT_WARPS * 32, smem, stream>>>(               \
+        diff_attention_tile_kernel<CT, OT, VCN><<<grid, DT_WARPS * 32, smem, stream>>>(          \
             (OT*)out, out_ld, q, (const CT*)cache, block_table, seq_of_token, positions,         \
             n_tokens, heads, kv_heads, dim, vdim, page_size, max_pages, num_pages, block, tq,    \
             scale, lambda, eps, out_scale, status);                                              \
+    } while (0)
+#define DIFFT(CT, OT)                                                                            \
+    do {                                                                                         \
+        switch ((vdim + 31) / 32) {         /* value coordinates a lane owns */                  \
+            case 1: DIFFT1(CT, OT, 1); break;                                                    \
+            case 2: DIFFT1(CT, OT, 2); break;                                                    \
+            case 3: DIFFT1(CT, OT, 3); break;                                                    \
+            default: DIFFT1(CT, OT, 4); break;                                                   \
+        }                                                                                        \
     } while (0)
     if (cache_dtype == PRB_F32 && out_dtype == PRB_F32) DIFFT(float, float);
     else if (cache_dtype == PRB_BF16 && out_dtype == PRB_BF16) DIFFT(__nv_bfloat16, __nv_bfloat16);
     else return PRB_E_DTYPE;
 #undef DIFFT
+#undef DIFFT1
     PRB_LAUNCH_CHECK();
     return 0;
 }

@@ -61,7 +61,7 @@ def expected_tensors(cfg: PezaraxConfig) -> Dict[str, TensorExpectation]:
 def random_tensors(cfg: PezaraxConfig, seed: int) -> Dict[str, torch.Tensor]:
     """Seeded initialisation: matrices N(0, 1/in), the token table N(0, 1) / embedding scale
     (so that the stream starts near unit size), norm weights 1 + N(0, 0.1), the lambda vectors
-    N(0, 0.3 / sqrt(dim)), routers N(0, 4/in) (scores that spread); every tensor from a generator
+    N(0, 0.3 / dim^(1/4)) (their dot products stay small), routers N(0, 4/in) (scores that spread); every tensor from a generator
     of its own."""
     out: Dict[str, torch.Tensor] = {}
     for name, exp in expected_tensors(cfg).items():
@@ -70,7 +70,7 @@ def random_tensors(cfg: PezaraxConfig, seed: int) -> Dict[str, torch.Tensor]:
         elif name.endswith(("norm", "norm1", "norm2")):
             out[name] = normal(seed, name, exp.shape, 0.1, mean=1.0)
         elif name.endswith((".lq1", ".lk1", ".lq2", ".lk2")):
-            out[name] = normal(seed, name, exp.shape, 0.3 / math.sqrt(exp.shape[0]) ** 0.5)
+            out[name] = normal(seed, name, exp.shape, 0.3 * exp.shape[0] ** -0.25)
         elif name.endswith(".router"):
             out[name] = normal(seed, name, exp.shape, 2.0 / math.sqrt(exp.shape[-1]))
         else:
