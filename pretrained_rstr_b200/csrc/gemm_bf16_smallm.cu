@@ -259,11 +259,11 @@ __device__ __forceinline__ void norm_rows_staged(const Args& a, __nv_bfloat16* x
         }
     }
     if (live == R) {
-        norm_rows_any<R>(xrow, dst, gb, k, a.beta != nullptr, a.eps);
+        norm_rows_any<R>(xrow, dst, gb, k, a.beta != nullptr, a.eps, a.uncentred == 0);
     } else if (live > 0) {
 #pragma unroll
         for (int r = 0; r < R; ++r)
-            if (xrow[r] != nullptr) norm_row_any(xrow[r], dst[r], gb, k, a.beta != nullptr, a.eps);
+            if (xrow[r] != nullptr) norm_row_any(xrow[r], dst[r], gb, k, a.beta != nullptr, a.eps, a.uncentred == 0);
     }
     __syncthreads();
 }
@@ -579,7 +579,7 @@ int prb_gemm_smallm_check(const void* x, const float* xf, const float* gamma, co
 }
 
 // x: bfloat16 [M,K] (xf null), or xf: float32 rows to be LayerNorm-ed first with gamma, beta
-// (may be null) and eps: row t of the product from row xf_rows[t] of xf's xf_rows_in rows
+// (may be null) and eps (uncentred: the mean is not taken off, a root-mean-square norm): row t of the product from row xf_rows[t] of xf's xf_rows_in rows
 // (xf_rows null: from row t).  m <= 64, k % 8 == 0, pitches multiples of 8 (4 for xf).
 // kv_width > 0: the product is a fused QKV projection and its key and value columns are
 // also written to the paged cache at slots[token] (the cache has the output's element type).
@@ -589,7 +589,8 @@ PRB_API int prb_gemm_smallm(void* out, const void* x, const float* xf, const int
                             const float* resid, int m, int n, int k, long ldx, long ldw, long ldc,
                             int act, int out_dtype, void* k_pages, void* v_pages,
                             const int* slots, int q_width, int kv_width, int head_dim,
-                            int page_size, int num_pages, int* status, cudaStream_t stream) {
+                            int page_size, int num_pages, int uncentred, int* status,
+                            cudaStream_t stream) {
     if (m <= 0 || n <= 0) return 0;
     const int bad = prb_gemm_smallm_check(x, xf, gamma, beta, w, m, n, k, ldx, ldw);
     if (bad) return bad;
@@ -602,6 +603,7 @@ PRB_API int prb_gemm_smallm(void* out, const void* x, const float* xf, const int
     a.gamma = gamma;
     a.beta = beta;
     a.eps = eps;
+    a.uncentred = uncentred ? 1 : 0;
     a.w = (const __nv_bfloat16*)w;
     a.bias = bias;
     a.resid = resid;

@@ -37,6 +37,7 @@ struct Args {
     const float* gamma;
     const float* beta;
     float eps;
+    int uncentred;                  // 1: the mean is not taken off (a root-mean-square norm)
     const __nv_bfloat16* w;         // [N,K]
     const float* bias;
     const float* resid;
@@ -89,7 +90,7 @@ __host__ __device__ inline size_t smem_bytes(int mt, bool ln, int k) {
 template <int NV, int R>
 __device__ __forceinline__ void norm_rows_of_warp(const float* const (&xrow)[R],
                                                   __nv_bfloat16* const (&dst)[R], const float* gb,
-                                                  int k, bool has_beta, float eps) {
+                                                  int k, bool has_beta, float eps, bool centred) {
     const int lane = threadIdx.x & 31;
     const int nvec = k / 4;
     float4 v[R][NV];
@@ -109,7 +110,7 @@ __device__ __forceinline__ void norm_rows_of_warp(const float* const (&xrow)[R],
         s[r] = 0.0f;
 #pragma unroll
         for (int i = 0; i < NV; ++i) s[r] += (v[r][i].x + v[r][i].y) + (v[r][i].z + v[r][i].w);
-        mean[r] = prb_warp_sum(s[r]) / (float)k;
+        mean[r] = centred ? prb_warp_sum(s[r]) / (float)k : 0.0f;    // (uncentred: x / rms(x))
     }
 #pragma unroll
     for (int r = 0; r < R; ++r) {
@@ -153,25 +154,25 @@ __device__ __forceinline__ void norm_rows_of_warp(const float* const (&xrow)[R],
 template <int R>
 __device__ __forceinline__ void norm_rows_any(const float* const (&xrow)[R],
                                               __nv_bfloat16* const (&dst)[R], const float* gb, int k,
-                                              bool has_beta, float eps) {
+                                              bool has_beta, float eps, bool centred) {
     const int iters = (k / 4 + 31) / 32;
-    if (iters <= 2) norm_rows_of_warp<2, R>(xrow, dst, gb, k, has_beta, eps);
-    else if (iters <= 6) norm_rows_of_warp<6, R>(xrow, dst, gb, k, has_beta, eps);
-    else if (iters <= 8) norm_rows_of_warp<8, R>(xrow, dst, gb, k, has_beta, eps);
+    if (iters <= 2) norm_rows_of_warp<2, R>(xrow, dst, gb, k, has_beta, eps, centred);
+    else if (iters <= 6) norm_rows_of_warp<6, R>(xrow, dst, gb, k, has_beta, eps, centred);
+    else if (iters <= 8) norm_rows_of_warp<8, R>(xrow, dst, gb, k, has_beta, eps, centred);
     else {
 #pragma unroll
         for (int r = 0; r < R; ++r) {
             const float* const one_x[1] = {xrow[r]};
             __nv_bfloat16* const one_d[1] = {dst[r]};
-            norm_rows_of_warp<LN_MAX_K / 128, 1>(one_x, one_d, gb, k, has_beta, eps);
+            norm_rows_of_warp<LN_MAX_K / 128, 1>(one_x, one_d, gb, k, has_beta, eps, centred);
         }
     }
 }
 __device__ __forceinline__ void norm_row_any(const float* xrow, __nv_bfloat16* dst, const float* gb,
-                                             int k, bool has_beta, float eps) {
+                                             int k, bool has_beta, float eps, bool centred) {
     const float* const one_x[1] = {xrow};
     __nv_bfloat16* const one_d[1] = {dst};
-    norm_rows_any<1>(one_x, one_d, gb, k, has_beta, eps);
+    norm_rows_any<1>(one_x, one_d, gb, k, has_beta, eps, centred);
 }
 
 __device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
@@ -231,7 +232,7 @@ __device__ __forceinline__ void norm_rows(const Args& a, __nv_bfloat16* xs) {
             v[i] = idx < nvec ? src[idx] : make_float4(0.f, 0.f, 0.f, 0.f);
             s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
         }
-        const float mean = prb_warp_sum(s) / (float)k;
+        const float mean = a.uncentred ? 0.0f : prb_warp_sum(s) / (float)k;
         float sq = 0.0f;
 #pragma unroll
         for (int i = 0; i < LN_MAX_K / 128; ++i) {

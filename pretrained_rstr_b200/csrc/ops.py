@@ -91,7 +91,7 @@ def _declare(h: ctypes.CDLL) -> None:
     h.prb_gemm_midm.argtypes = [P, P, P, P, P, I, I, I, L, L, L, I, I, P, P]
     h.prb_gemm_midm_supports.argtypes = [I, I, I]
     h.prb_gemm_smallm.argtypes = [P, P, P, P, I, P, P, F, P, P, P, I, I, I, L, L, L, I, I,
-                                  P, P, P, I, I, I, I, I, P, P]
+                                  P, P, P, I, I, I, I, I, I, P, P]
     h.prb_gemm_smallm_max_rows.argtypes = []
     h.prb_gemm_smallm_max_norm_width.argtypes = []
     h.prb_attention_generic.argtypes = [P, L, P, L, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I,
@@ -459,10 +459,12 @@ def smallm_limits():
 
 
 def gemm_smallm(out, w, a=None, norm_input=None, gamma=None, beta=None, eps=0.0, bias=None,
-                resid=None, act=None, kv_scatter=None, status=None, norm_rows=None) -> None:
+                resid=None, act=None, kv_scatter=None, status=None, norm_rows=None,
+                centred: bool = True) -> None:
     """out[M,N] = act(X . w[N,K]^T + bias) (+ resid) for M <= 64 rows, weights streamed once.
     X is ``a`` (bfloat16 [M,K]) or LayerNorm(``norm_input``) (float32 [M,K]) with ``gamma``,
-    ``beta`` and ``eps``, the norm fused into the kernel; with ``norm_rows`` (int32 [M]) row t
+    ``beta`` and ``eps`` (``centred`` False: the mean is not taken off, i.e. x / sqrt(mean(x^2)
+    + eps) * gamma, a root-mean-square norm), the norm fused into the kernel; with ``norm_rows`` (int32 [M]) row t
     of X is the norm of row norm_rows[t] of ``norm_input`` (an index outside it gives a zero
     row and is recorded in ``status``).  ``kv_scatter`` = (k_pages, v_pages,
     slots, q_width): the product is a fused QKV projection; its key and value columns are also
@@ -511,7 +513,7 @@ def gemm_smallm(out, w, a=None, norm_input=None, gamma=None, beta=None, eps=0.0,
         _p(x) if norm_input is not None else None, _p(norm_rows),
         x.shape[0] if norm_input is not None else 0, _p(gamma), _p(beta), float(eps), _p(w),
         _p(bias), _p(resid), m, n, k, x.stride(0), w.stride(0), out.stride(0), ACT_CODES[act],
-        dtype_code(out.dtype), *kv, _p(status), _stream()), what)
+        dtype_code(out.dtype), *kv, 0 if centred else 1, _p(status), _stream()), what)
 
 
 def attention_generic(out, q, k_pages, v_pages, block_table, seq_of_token, positions, n_tokens,

@@ -34,6 +34,7 @@ from .registry import register_part
 class DifferentialAttention(Mixer):
     graph_safe = True
     can_overwrite = True
+    accepts_lazy_norm = True      # the first matrix product may compute the norm itself
 
     def __init__(self, p: dict, store, runtime):
         w = p["weights"]

@@ -174,6 +174,7 @@ class RoutedExperts(FeedForward):
     sizes, cheap while experts are small."""
     graph_safe = True
     can_overwrite = True
+    accepts_lazy_norm = True      # the first matrix product may compute the norm itself
 
     def __init__(self, p: dict, store, runtime):
         from .latent_attention import FusedInput

@@ -80,7 +80,7 @@ class Linear:
                 ops.gemm_smallm(out, self.weight, norm_input=a.x, gamma=a.norm.gamma,
                                 beta=a.norm.beta, eps=a.norm.eps, bias=self.bias, resid=resid,
                                 act=act, kv_scatter=kv_scatter, status=ctx.status,
-                                norm_rows=a.rows)
+                                norm_rows=a.rows, centred=getattr(a.norm, "centred", True))
             else:
                 ops.gemm_smallm(out, self.weight, a=_tensor(a), bias=self.bias, resid=resid,
                                 act=act, kv_scatter=kv_scatter, status=ctx.status)
@@ -109,14 +109,17 @@ def padded_linear(weight: torch.Tensor, runtime) -> Linear:
 class LazyNorm:
     """A norm of ``x`` (of its rows ``rows``, if given: an int32 tensor of row indices) that
     runs when its result is first needed.  A consumer that can compute the norm itself
-    (``fusable``: a plain layer norm) reads ``x``, ``rows`` and ``norm`` instead and the norm
+    (``fusable``: a plain layer norm, or a root-mean-square norm that is a weight per coordinate
+    times x / rms(x)) reads ``x``, ``rows`` and ``norm`` instead and the norm
     never runs as a kernel of its own."""
 
     def __init__(self, ctx, norm, x: torch.Tensor, out: torch.Tensor, rows=None):
         self.ctx, self.norm, self.x, self._out, self.rows = ctx, norm, x, out, rows
         self._done = False
+        # (a layer norm, or a root-mean-square norm with a weight per coordinate and no other
+        # factor: the same prologue without the mean)
         self.fusable = all(hasattr(norm, f) for f in ("gamma", "beta", "eps")) and \
-            getattr(norm, "kind", "") == "layer_norm"
+            getattr(norm, "kind", "") in ("layer_norm", "rms_norm") and norm.gamma is not None
         self.shape = out.shape
 
     def tensor(self) -> torch.Tensor:

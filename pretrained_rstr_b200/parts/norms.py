@@ -47,6 +47,12 @@ class RMSNorm(Norm):
         self.gain = None if gain is None else gain.to(torch.float32).reshape(1).contiguous()
         self.weight = None if weight is None else weight.to(torch.float32).contiguous()
         self.eps, self.size = float(eps), size
+        # what the decode-time product's fused prologue needs to compute this norm itself: the
+        # layer norm's names, without a mean and a bias (only when a weight per coordinate is
+        # the norm's one factor)
+        self.gamma = self.weight if self.gain is None else None
+        self.beta = None
+        self.centred = False
 
     def forward(self, ctx, x, out, rows=None) -> None:
         ops.rms_norm(x, out=out, gain=self.gain, weight=self.weight, rows=rows, eps=self.eps,

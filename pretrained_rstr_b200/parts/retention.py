@@ -29,6 +29,7 @@ from .registry import register_part
 class Retention(Mixer):
     graph_safe = True
     can_overwrite = True
+    accepts_lazy_norm = True      # the first matrix product may compute the norm itself
 
     def __init__(self, p: dict, store, runtime):
         w = p["weights"]
