@@ -170,6 +170,13 @@ def _declare(h: ctypes.CDLL) -> None:
     h.prb_diff_attention_single.argtypes = [P, L, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, F, F,
                                             F, I, I, P, P]
     h.prb_diff_attention_single.restype = c_int
+    h.prb_route_act.argtypes = [P, L, P, L, I, I, I, I, I, I, I, I, I, I, P, I, P]
+    h.prb_route_act.restype = c_int
+    h.prb_retention_step_supports.argtypes = [I, I]
+    h.prb_retention_step_supports.restype = c_int
+    h.prb_retention_step.argtypes = [P, L, P, L, I, I, I, I, P, P, P, P, P, P, I, I, I, I, I, I, I,
+                                     F, F, I, P, P]
+    h.prb_retention_step.restype = c_int
     for name in ("prb_embed_scaled", "prb_route_scores", "prb_routed_act", "prb_retention_lanes",
                  "prb_retention_scan", "prb_retention_finish", "prb_diff_prepare",
                  "prb_diff_attention"):
@@ -1201,7 +1208,66 @@ def routed_act(out, inp, in_col: int, n: int, weights, group: int, act: str = "r
                                 dtype_code(out.dtype), _stream()), what)
 
 
+def route_act(out, inp, in_col: int, router_col: int, experts: int, top: int, group: int,
+              score: str = "sigmoid", renormalize: bool = False, act: str = "relu_squared",
+              weight_on: str = "input", weights_out=None) -> None:
+    """:func:`route_scores` (of the logits at columns ``router_col`` .. of ``inp``) and
+    :func:`routed_act` (of the ``experts * group`` columns from ``in_col`` on) in one launch, a
+    CTA per row.  ``weights_out`` (optional, float32 [rows, experts]) receives the weights."""
+    what = "route_act"
+    if not inp.is_cuda or inp.dtype != torch.float32 or inp.stride(1) != 1:
+        raise KernelArgumentError(f"{what}: inp must be float32 on CUDA with unit inner stride")
+    n = experts * group
+    if not out.is_cuda or out.stride(1) != 1 or out.shape[0] < inp.shape[0] or n > out.shape[1] \
+            or in_col + n > inp.shape[1] or router_col + experts > inp.shape[1]:
+        raise KernelArgumentError(f"{what}: columns outside the tensors")
+    if weights_out is not None:
+        _need(weights_out, torch.float32, "weights_out", what)
+        if weights_out.shape != (inp.shape[0], experts):
+            raise KernelArgumentError(f"{what}: weights_out must be [rows, experts]")
+    _check(lib().prb_route_act(_p(out), out.stride(0), _p(inp), inp.stride(0), int(in_col),
+                               int(router_col), inp.shape[0], int(experts), int(top),
+                               SCORE_CODES[score], 1 if renormalize else 0, int(group),
+                               ROUTED_ACT_CODES[act], 1 if weight_on == "output" else 0,
+                               _p(weights_out), dtype_code(out.dtype), _stream()), what)
+
+
 # ------------------------------------------------------------------------ retention
+def retention_step_supports(dim: int, vdim: int) -> bool:
+    """Whether the one-launch form of a retention step takes these sizes."""
+    return bool(lib().prb_retention_step_supports(int(dim), int(vdim)))
+
+
+def retention_step(out, proj, q_col: int, k_col: int, v_col: int, g_col: int, state, q_start,
+                   state_slot, positions, decay, freq, n_requests: int, heads: int, dim: int,
+                   vdim: int, rot_dims: int, k_scale: float, eps: float, status=None) -> None:
+    """Rotation, recurrence and finish (:func:`retention_scan` and :func:`retention_finish`) of
+    a step of few tokens in ONE launch, a CTA per (head, request); ``proj`` is not changed.
+    ``g_col`` < 0: no gate.  out in the activation type, rows may be wider than heads * vdim."""
+    what = "retention_step"
+    _need(state, torch.float32, "state", what)
+    _need(decay, torch.float32, "decay", what)
+    _need(freq, torch.float32, "freq", what)
+    for name, t in (("q_start", q_start), ("state_slot", state_slot), ("positions", positions)):
+        _need(t, torch.int32, name, what)
+    if not proj.is_cuda or proj.dtype != torch.float32 or proj.stride(1) != 1:
+        raise KernelArgumentError(f"{what}: proj must be float32 on CUDA with unit inner stride")
+    n = proj.shape[0]
+    if not out.is_cuda or out.stride(1) != 1 or out.shape[0] < n or out.shape[1] < heads * vdim or \
+            decay.numel() != heads or tuple(state.shape[1:]) != (heads, vdim, dim) or \
+            q_start.numel() < n_requests + 1 or state_slot.numel() < n_requests or \
+            freq.numel() < max(1, rot_dims // 2) or \
+            max(q_col, k_col) + heads * dim > proj.shape[1] or \
+            max(v_col, g_col) + heads * vdim > proj.shape[1]:
+        raise KernelArgumentError(f"{what}: shapes do not fit")
+    _check(lib().prb_retention_step(_p(out), out.stride(0), _p(proj), proj.stride(0), int(q_col),
+                                    int(k_col), int(v_col), int(g_col), _p(state), _p(q_start),
+                                    _p(state_slot), _p(positions), _p(decay), _p(freq), n,
+                                    int(n_requests), state.shape[0], heads, dim, vdim,
+                                    int(rot_dims), float(k_scale), float(eps),
+                                    dtype_code(out.dtype), _p(status), _stream()), what)
+
+
 def retention_lanes(dim: int) -> int:
     """Lanes the scan spreads a state column over (0: a head size it does not take)."""
     return int(lib().prb_retention_lanes(int(dim)))

@@ -234,6 +234,120 @@ __global__ void retention_carry_kernel(ScanArgs a) {
     }
 }
 
+// Steps of few tokens: ONE launch instead of three.  A CTA per (head, request) holds all of the
+// head's value columns (vdim * lanes threads), rotates q and k of its tokens itself, runs the
+// recurrence from and to the slot, and finishes every token in place: unit RMS over the head's
+// values, the gate, the activation type.  The sums are those of the three kernels, in their order.
+struct StepArgs {
+    ScanArgs scan;            // cols == vdim
+    const float* freq;
+    int rot_dims;
+    float k_scale, eps;
+    void* out;                // [T, out_ld] in O
+    long out_ld;
+    int g_col;                // column of the gate in proj, or -1
+};
+
+template <int RET_NI, typename O>
+__global__ void retention_step_kernel(StepArgs sa) {
+    extern __shared__ __align__(16) float smem[];
+    __shared__ float inv_s;
+    const ScanArgs& a = sa.scan;
+    prb_grid_launch_dependents();
+    const int h = blockIdx.x, b = blockIdx.y;
+    const int t0 = a.q_start[b], t1 = a.q_start[b + 1];
+    if (t1 <= t0 || t0 < 0 || t1 > a.n_tokens) return;
+    const int R = a.lanes, dim_pad = R * RET_NI;
+    float* qs = smem;                               // [dim_pad]
+    float* ks = qs + dim_pad;                       // [dim_pad]
+    float* os = ks + dim_pad;                       // [vdim]
+    const int r = threadIdx.x % R, col = threadIdx.x / R;
+    const bool live = col < a.vdim;
+    const int slot = a.state_slot[b];
+    if (slot < 0 || slot >= a.n_slots) {
+        if (threadIdx.x == 0) prb_set_status(a.status, PRB_S_SLOT_RANGE, t0, slot, a.n_slots);
+        return;
+    }
+    float* srow = a.state + (((size_t)slot * a.heads + h) * a.vdim + (live ? col : 0)) * a.dim;
+    const bool carried = a.positions[t0] > 0;
+    float S[RET_NI];
+#pragma unroll
+    for (int ii = 0; ii < RET_NI; ++ii) {
+        const int i = r * RET_NI + ii;
+        S[ii] = (live && carried && i < a.dim) ? srow[i] : 0.0f;
+    }
+    const float decay = a.decay[h];
+    const int half = sa.rot_dims / 2;
+    const int units = half + (a.dim - sa.rot_dims);
+    O* out = reinterpret_cast<O*>(sa.out);
+    for (int t = t0; t < t1; ++t) {
+        __syncthreads();                            // the token before is done with shared memory
+        const float* row = a.proj + (size_t)t * a.ld;
+        const float* qr = row + a.q_col + h * a.dim;
+        const float* kr = row + a.k_col + h * a.dim;
+        const float pos = (float)a.positions[t];
+        for (int w = threadIdx.x; w < units; w += blockDim.x) {
+            if (w < half) {
+                float sn, cs;
+                sincosf(pos * sa.freq[w], &sn, &cs);
+                const float q0 = qr[w], q1 = qr[w + half], k0 = kr[w], k1 = kr[w + half];
+                qs[w] = q0 * cs - q1 * sn;
+                qs[w + half] = q1 * cs + q0 * sn;
+                ks[w] = (k0 * cs - k1 * sn) * sa.k_scale;
+                ks[w + half] = (k1 * cs + k0 * sn) * sa.k_scale;
+            } else {
+                const int i = w - half + sa.rot_dims;
+                qs[i] = qr[i];
+                ks[i] = kr[i] * sa.k_scale;
+            }
+        }
+        for (int i = a.dim + threadIdx.x; i < dim_pad; i += blockDim.x) qs[i] = ks[i] = 0.0f;
+        __syncthreads();
+        const float v = live ? row[a.v_col + h * a.vdim + col] : 0.0f;
+        const float4* q4 = reinterpret_cast<const float4*>(qs + r * RET_NI);
+        const float4* k4 = reinterpret_cast<const float4*>(ks + r * RET_NI);
+        float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+        for (int g = 0; g < RET_NI / 4; ++g) {
+            const float4 kk = k4[g], qq = q4[g];
+            S[4 * g + 0] = fmaf(decay, S[4 * g + 0], kk.x * v);
+            S[4 * g + 1] = fmaf(decay, S[4 * g + 1], kk.y * v);
+            S[4 * g + 2] = fmaf(decay, S[4 * g + 2], kk.z * v);
+            S[4 * g + 3] = fmaf(decay, S[4 * g + 3], kk.w * v);
+            acc[0] = fmaf(S[4 * g + 0], qq.x, acc[0]);
+            acc[1] = fmaf(S[4 * g + 1], qq.y, acc[1]);
+            acc[2] = fmaf(S[4 * g + 2], qq.z, acc[2]);
+            acc[3] = fmaf(S[4 * g + 3], qq.w, acc[3]);
+        }
+        float o = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+        for (int m = 1; m < R; m <<= 1) o += __shfl_xor_sync(0xffffffffu, o, m);
+        if (live && r == 0) os[col] = o;
+        __syncthreads();
+        if (threadIdx.x < 32) {                     // the head's unit RMS, as retention_finish sums it
+            float ss = 0.0f;
+            for (int j = threadIdx.x; j < a.vdim; j += 32) ss = fmaf(os[j], os[j], ss);
+            ss = prb_warp_sum(ss);
+            if (threadIdx.x == 0) inv_s = 1.0f / sqrtf(ss / (float)a.vdim + sa.eps);
+        }
+        __syncthreads();
+        if (live && r == 0) {
+            float y = o * inv_s;
+            if (sa.g_col >= 0) {
+                const float z = row[sa.g_col + h * a.vdim + col];
+                y *= z / (1.0f + expf(-z));
+            }
+            out[(size_t)t * sa.out_ld + h * a.vdim + col] = prb_from_float<O>(y);
+        }
+    }
+    if (live) {
+#pragma unroll
+        for (int ii = 0; ii < RET_NI; ++ii) {
+            const int i = r * RET_NI + ii;
+            if (i < a.dim) srow[i] = S[ii];
+        }
+    }
+}
+
 template <typename O>
 __global__ void retention_finish_kernel(O* __restrict__ out, long out_ld, const float* __restrict__ o_raw,
                                         const float* __restrict__ proj, long ld, int g_col,
@@ -366,6 +480,47 @@ PRB_API int prb_retention_finish(void* out, long out_ld, const float* o_raw, con
             (__nv_bfloat16*)out, out_ld, o_raw, proj, ld, g_col, seq, n_tokens, heads, vdim, eps);
     else
         return PRB_E_DTYPE;
+    PRB_LAUNCH_CHECK();
+    return 0;
+}
+
+// 1 when the one-launch form takes these sizes (all of a head's columns in one CTA).
+PRB_API int prb_retention_step_supports(int dim, int vdim) {
+    const int lanes = prb_retention_lanes(dim);
+    return lanes > 0 && (long)vdim * lanes <= 1024 ? 1 : 0;
+}
+
+// Rotation, recurrence and finish of a step of few tokens in one launch (see
+// retention_step_kernel); out in the activation type, its rows out_ld apart.
+PRB_API int prb_retention_step(void* out, long out_ld, const float* proj, long ld, int q_col,
+                               int k_col, int v_col, int g_col, float* state, const int* q_start,
+                               const int* state_slot, const int* positions, const float* decay,
+                               const float* freq, int n_tokens, int n_requests, int n_slots,
+                               int heads, int dim, int vdim, int rot_dims, float k_scale, float eps,
+                               int out_dtype, int* status, cudaStream_t stream) {
+    if (n_tokens <= 0 || n_requests <= 0) return 0;
+    const int lanes = prb_retention_lanes(dim);
+    if (heads <= 0 || heads > 65535 || n_requests > 65535 || dim <= 0 || vdim <= 0 ||
+        !prb_retention_step_supports(dim, vdim) || rot_dims < 0 || rot_dims > dim || rot_dims % 2 != 0)
+        return PRB_E_SIZE;
+    if (ld % 4 != 0 || ((uintptr_t)proj) % 16 != 0) return PRB_E_ALIGN;
+    const int ni = ret_ni(dim);
+    const int threads = (vdim * lanes + 31) / 32 * 32;
+    StepArgs sa{ScanArgs{nullptr, proj, ld, q_col, k_col, v_col, state, q_start, state_slot,
+                         positions, decay, n_tokens, n_slots, heads, dim, vdim, vdim, lanes, status,
+                         n_requests, 0, nullptr, nullptr},
+                freq, rot_dims, k_scale, eps, out, out_ld, g_col};
+    const size_t smem = (size_t)(2 * lanes * ni + vdim) * sizeof(float);
+    const dim3 grid(heads, n_requests);
+    if (out_dtype == PRB_F32) {
+        if (ni == 4) retention_step_kernel<4, float><<<grid, threads, smem, stream>>>(sa);
+        else retention_step_kernel<16, float><<<grid, threads, smem, stream>>>(sa);
+    } else if (out_dtype == PRB_BF16) {
+        if (ni == 4) retention_step_kernel<4, __nv_bfloat16><<<grid, threads, smem, stream>>>(sa);
+        else retention_step_kernel<16, __nv_bfloat16><<<grid, threads, smem, stream>>>(sa);
+    } else {
+        return PRB_E_DTYPE;
+    }
     PRB_LAUNCH_CHECK();
     return 0;
 }

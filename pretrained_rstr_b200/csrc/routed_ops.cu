@@ -156,6 +156,86 @@ __global__ void routed_act1_kernel(O* __restrict__ out, long out_ld, const float
     const float v = wgt == 0.0f ? 0.0f : (on_output ? wgt * routed_act(u, act) : routed_act(wgt * u, act));
     out[(size_t)t * out_ld + i] = prb_from_float<O>(v);
 }
+// ------------------------------------------------- router and activation in one launch
+// A CTA per token: the scores of the token's router logits (columns of the same 32-bit
+// product that holds the experts' first results), the choice, then the activation of the row
+// with the chosen experts' weights (the others' columns come out zero and are not read).
+template <typename O>
+__global__ void route_act_kernel(O* __restrict__ out, long out_ld, const float* __restrict__ in,
+                                 long in_ld, int in_col, int router_col, int n_rows, int n_experts,
+                                 int top, int score_fn, int renorm, int group, int act,
+                                 int on_output, float* __restrict__ weights_out) {
+    extern __shared__ float sh[];                // [n_experts] scores, then [n_experts] weights
+    float* sc = sh;
+    float* wt = sh + n_experts;
+    prb_grid_launch_dependents();
+    const int t = blockIdx.x;
+    if (t >= n_rows) return;
+    const float* row = in + (size_t)t * in_ld;
+    for (int e = threadIdx.x; e < n_experts; e += blockDim.x) {
+        const float z = row[router_col + e];
+        sc[e] = score_fn == 0 ? sigmoidf_(z) : z;
+        wt[e] = 0.0f;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float sum = 0.0f;
+        for (int k = 0; k < top; ++k) {
+            int arg = -1;
+            float best = -INFINITY;
+            for (int e = 0; e < n_experts; ++e) {
+                const float v = sc[e];
+                if (v == v && (arg < 0 || v > best)) { best = v; arg = e; }
+            }
+            if (arg < 0) break;                  // (a row of NaNs: padding, or a fault upstream)
+            wt[arg] = best;
+            sum += best;
+            sc[arg] = NAN;                       // taken
+        }
+        if (renorm)
+            for (int e = 0; e < n_experts; ++e) wt[e] /= sum;
+    }
+    __syncthreads();
+    if (weights_out)
+        for (int e = threadIdx.x; e < n_experts; e += blockDim.x) weights_out[(size_t)t * n_experts + e] = wt[e];
+    const int n = n_experts * group;
+    O* o = out + (size_t)t * out_ld;
+    const bool vec = group % 4 == 0 && in_col % 4 == 0 && in_ld % 4 == 0 && out_ld % 4 == 0 &&
+                     ((uintptr_t)in) % 16 == 0 && ((uintptr_t)out) % (4 * sizeof(O)) == 0;
+    if (vec) {
+        for (int i = threadIdx.x * 4; i < n; i += blockDim.x * 4) {
+            const float wgt = wt[i / group];
+            float v[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            if (wgt != 0.0f) {
+                const float4 u = *reinterpret_cast<const float4*>(row + in_col + i);
+                const float wi = on_output ? 1.0f : wgt, wo = on_output ? wgt : 1.0f;
+                v[0] = wo * routed_act(wi * u.x, act);
+                v[1] = wo * routed_act(wi * u.y, act);
+                v[2] = wo * routed_act(wi * u.z, act);
+                v[3] = wo * routed_act(wi * u.w, act);
+            }
+            if constexpr (sizeof(O) == 4) {
+                *reinterpret_cast<float4*>(o + i) = make_float4(v[0], v[1], v[2], v[3]);
+            } else {
+                const __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]), hi = __floats2bfloat162_rn(v[2], v[3]);
+                uint2 pk;
+                pk.x = *reinterpret_cast<const uint32_t*>(&lo);
+                pk.y = *reinterpret_cast<const uint32_t*>(&hi);
+                *reinterpret_cast<uint2*>(o + i) = pk;
+            }
+        }
+    } else {
+        for (int i = threadIdx.x; i < n; i += blockDim.x) {
+            const float wgt = wt[i / group];
+            float v = 0.0f;
+            if (wgt != 0.0f) {
+                const float u = row[in_col + i];
+                v = on_output ? wgt * routed_act(u, act) : routed_act(wgt * u, act);
+            }
+            o[i] = prb_from_float<O>(v);
+        }
+    }
+}
 }  // namespace
 
 PRB_API int prb_embed_scaled(float* out, float* keep, const int* tokens, const void* table,
@@ -227,6 +307,31 @@ PRB_API int prb_routed_act(void* out, long out_ld, const float* in, long in_ld, 
             routed_act1_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(
                 (__nv_bfloat16*)out, out_ld, in, in_ld, in_col, n, n_rows, weights, w_ld, group, act, on_output);
     }
+    PRB_LAUNCH_CHECK();
+    return 0;
+}
+
+// Router (logits at columns router_col.. of `in`) and the experts' activation (their first
+// results at columns in_col..) in one launch; `weights_out` (may be null): [rows, experts].
+PRB_API int prb_route_act(void* out, long out_ld, const float* in, long in_ld, int in_col,
+                          int router_col, int n_rows, int n_experts, int top, int score_fn,
+                          int renorm, int group, int act, int on_output, float* weights_out,
+                          int out_dtype, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (n_experts <= 0 || top <= 0 || top > n_experts || n_experts > 4096 || group <= 0)
+        return PRB_E_SIZE;
+    if (score_fn < 0 || score_fn > 1 || act < 0 || act > 3) return PRB_E_ARG;
+    const size_t smem = (size_t)2 * n_experts * sizeof(float);
+    if (out_dtype == PRB_F32)
+        route_act_kernel<float><<<n_rows, 256, smem, stream>>>(
+            (float*)out, out_ld, in, in_ld, in_col, router_col, n_rows, n_experts, top, score_fn,
+            renorm, group, act, on_output, weights_out);
+    else if (out_dtype == PRB_BF16)
+        route_act_kernel<__nv_bfloat16><<<n_rows, 256, smem, stream>>>(
+            (__nv_bfloat16*)out, out_ld, in, in_ld, in_col, router_col, n_rows, n_experts, top,
+            score_fn, renorm, group, act, on_output, weights_out);
+    else
+        return PRB_E_DTYPE;
     PRB_LAUNCH_CHECK();
     return 0;
 }

@@ -214,14 +214,12 @@ class RoutedExperts(FeedForward):
         t = x.shape[0]
         cap = ctx.token_capacity
         proj = self._proj = self.input.run(ctx, h)
-        weights = ctx.scratch("routed_weights", (cap, self.experts), torch.float32)[:t]
-        chosen = ctx.scratch("routed_chosen", (cap, self.top), torch.int32)[:t]
-        chosen_w = ctx.scratch("routed_chosen_w", (cap, self.top), torch.float32)[:t]
-        ops.route_scores(weights, chosen, chosen_w, self.input.view(proj, "router"), None,
-                         self.top, self.score, self.renormalize)
+        # the router's scores, the choice and the activation with the chosen experts' weights:
+        # one launch, a CTA per token
         a = ctx.scratch_zero("routed_act", (cap, self.down.n_in), self.runtime.dtype)[:t]
-        ops.routed_act(a, proj, self.input.cols["up"][0], self.experts * self.inner, weights,
-                       self.inner, self.activation, self.weight_on)
+        ops.route_act(a, proj, self.input.cols["up"][0], self.input.cols["router"][0], self.experts,
+                      self.top, self.inner, self.score, self.renormalize, self.activation,
+                      self.weight_on)
         self.down.forward(ctx, a, x, resid=x if accumulate else None)
 
 

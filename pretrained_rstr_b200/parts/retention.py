@@ -65,6 +65,7 @@ class Retention(Mixer):
         self.decay = torch.tensor(decay, dtype=torch.float64).to(torch.float32).to(dev)
         self.freq = rotary_frequencies(float(p.get("rot_base", 10000.0)), self.rot_dims, dev)
         self.sm_count = ops.sm_count() if torch.cuda.is_available() else 148
+        self.one_launch = torch.cuda.is_available() and ops.retention_step_supports(self.dim, self.vdim)
 
     def state_specs(self):
         return [StateSpec("retention", (self.heads, self.vdim, self.dim), torch.float32)]
@@ -88,8 +89,18 @@ class Retention(Mixer):
         cap = ctx.token_capacity
         proj = self._proj = self.input.run(ctx, h)
         cols = self.input.cols
-        raw = ctx.scratch("retention_raw", (cap, self.heads * self.vdim), torch.float32)[:t]
         requests = ctx.layout.b_cap
+        gated = ctx.scratch_zero("retention_gated", (cap, self.out.n_in), self.runtime.dtype)[:t]
+        if ctx.layout.t_cap <= ops.retention_segment() and self.one_launch:
+            # a step of few tokens: rotation, recurrence and finish in one launch
+            ops.retention_step(gated, proj, cols["q"][0], cols["k"][0], cols["v"][0],
+                               cols["gate"][0] if self.gated else -1, cache.state["retention"],
+                               ctx.q_start, ctx.state_slot, ctx.positions, self.decay, self.freq,
+                               requests, self.heads, self.dim, self.vdim, self.rot_dims,
+                               self.k_scale, self.eps, ctx.status)
+            self.out.forward(ctx, gated, x, resid=x if accumulate else None)
+            return
+        raw = ctx.scratch("retention_raw", (cap, self.heads * self.vdim), torch.float32)[:t]
         # a step with room for more tokens than a segment: portions are cut into segments that
         # run side by side (workspaces sized once, for the largest step the runtime takes)
         segments = None
@@ -105,7 +116,6 @@ class Retention(Mixer):
                            self.decay, self.freq, requests, self.heads, self.dim, self.vdim,
                            self.rot_dims, self.k_scale, self._columns_per_cta(lists), ctx.status,
                            segments=segments)
-        gated = ctx.scratch_zero("retention_gated", (cap, self.out.n_in), self.runtime.dtype)[:t]
         ops.retention_finish(gated, raw, proj if self.gated else None,
                              cols["gate"][0] if self.gated else 0, ctx.seq_of_token, self.heads,
                              self.vdim, self.eps)

@@ -210,6 +210,26 @@ def test_router_and_expert_activation_kernels():
                 assert torch.allclose(out.cpu().float()[:, :n_cols], wide * fn(u), atol=tol, rtol=tol)
 
 
+def test_router_and_activation_in_one_launch():
+    """The fused kernel against the two it replaces, with and without 16-byte loads."""
+    from pretrained_rstr_b200.csrc import ops
+    g = torch.Generator().manual_seed(13)
+    for t, n_e, ff, top, col in ((9, 6, 12, 2, 8), (5, 3, 10, 1, 4), (40, 16, 24, 16, 4)):
+        inp = (torch.randn(t, col + n_e * ff + 8 + n_e, generator=g) * 2).to(DEV)
+        rcol = col + n_e * ff + 8
+        weights = torch.empty(t, n_e, device=DEV)
+        chosen = torch.empty(t, top, dtype=torch.int32, device=DEV)
+        chosen_w = torch.empty(t, top, device=DEV)
+        ops.route_scores(weights, chosen, chosen_w, inp[:, rcol:rcol + n_e], None, top)
+        for dtype in (torch.float32, torch.bfloat16):
+            want = torch.full((t, n_e * ff + 8), 3.0, dtype=dtype, device=DEV)
+            got = torch.full((t, n_e * ff + 8), 3.0, dtype=dtype, device=DEV)
+            w2 = torch.empty(t, n_e, device=DEV)
+            ops.routed_act(want, inp, col, n_e * ff, weights, ff)
+            ops.route_act(got, inp, col, rcol, n_e, top, ff, weights_out=w2)
+            assert torch.equal(got, want) and torch.equal(w2, weights)
+
+
 class RetentionCase:
     """Hand-made q, k, v (and gate) rows behind a stand-in for the fused projection."""
 
@@ -232,9 +252,10 @@ class RetentionCase:
         gd = gate.double()
         return P.unit_rms(o, eps) * gd * torch.sigmoid(gd)
 
-    def run(self, parts, eps, cols, out_dtype=torch.float32, segmented=False):
+    def run(self, parts, eps, cols, out_dtype=torch.float32, segmented=False, one_launch=False):
         """parts: (slot, first position, q, k, v, gate) per request of one step; ``segmented``:
-        portions cut into segments that run side by side."""
+        portions cut into segments that run side by side; ``one_launch``: rotation, recurrence
+        and finish in one kernel."""
         from pretrained_rstr_b200.csrc import ops
         from pretrained_rstr_b200.parts.positions_rotary import rotary_frequencies
         h, d, vd = self.heads, self.dim, self.vdim
@@ -254,6 +275,14 @@ class RetentionCase:
         status = torch.zeros(4, dtype=torch.int32, device=DEV)
         decay = torch.tensor(self.decay, dtype=torch.float32, device=DEV)
         freq = rotary_frequencies(self.base, self.rot_dims, DEV)
+        if one_launch:
+            assert ops.retention_step_supports(d, vd)
+            out = torch.zeros(t, h * vd + 8, dtype=out_dtype, device=DEV)
+            ops.retention_step(out, proj, 4, 4 + h * d, 8 + 2 * h * d, 8 + 2 * h * d + h * vd, self.state,
+                               _i32(qs + [qs[-1]]), _i32(slots + [0]), _i32(pos), decay, freq,
+                               len(parts) + 1, h, d, vd, self.rot_dims, self.k_scale, eps, status)
+            assert int(status[0]) == 0
+            return out.cpu().double()[:, :h * vd].reshape(t, h, vd)
         segments = None
         if segmented:
             n = ops.retention_max_segments(t, len(parts) + 1)
@@ -272,6 +301,7 @@ class RetentionCase:
 def test_retention_kernels(heads, dim, vdim, rot_dims):
     """A whole sequence at once, in portions down to one token, beside another request, in any
     split of the value columns over CTAs; a slot's earlier state is not read at position 0."""
+    from pretrained_rstr_b200.csrc import ops
     decay = [1.0 - 2.0 ** -(3 + 2 * j) for j in range(heads)]
     case = RetentionCase(heads, dim, vdim, rot_dims, 50.0, decay, seed=heads)
     n = 90
@@ -300,7 +330,8 @@ def test_retention_kernels(heads, dim, vdim, rot_dims):
         m = 1 + at % 7
         other = (2, 0, q2[:m], k2[:m], v2[:m], gate2[:m])
         parts = [other, part] if at % 2 else [part, other]
-        got = case.run(parts, 1e-5, cols=8 if size % 2 else 5)
+        got = case.run(parts, 1e-5, cols=8 if size % 2 else 5,
+                       one_launch=size in (2, 16, 20) and ops.retention_step_supports(dim, vdim))
         r0 = m if at % 2 else 0
         outs.append(got[r0:r0 + size])
         other_rows = got[:m] if at % 2 else got[size:]
