@@ -46,12 +46,13 @@ def _model(vocab, width, layers, loop=None, scale=5.0, logit_scale=1.0, eps=1e-6
 # powers of two; a layer without a feed-forward; one, some and all experts chosen; rotations that
 # cover a part, all or nothing of a head; blocks shorter and longer than a page and than the
 # kernel's key segment; a loop in the middle, a loop from the first layer on, no loop; a model
-# without attention (no pages at all) and one whose first layer is attention.
+# without attention (no pages at all) and one whose first layer is attention; two, three and
+# eight query heads a key/value head (eight: more than the single-token kernel takes).
 SHAPE_A = _model(300, 64, [
     _ret(2, 16, 24, [0.9, 0.99], _moe(5, 2, 24), rot_dims=8),
     _att(4, 2, 16, 24, 20, _moe(3, 1, 40), rot_dims=12, diff=0.25),
     _ret(4, 8, 16, [0.5, 0.97, 0.999, 1.0], None),
-    _att(2, 2, 24, 8, 70, _moe(4, 4, 16), base=300.0, scale=0.3)], loop=(1, 3, 2), logit_scale=0.6)
+    _att(8, 1, 24, 8, 70, _moe(4, 4, 16), base=300.0, scale=0.3)], loop=(1, 3, 2), logit_scale=0.6)
 SHAPE_B = _model(515, 128, [
     _att(3, 1, 40, 56, 300, _moe(6, 3, 24), rot_dims=0, diff=0.4),
     _ret(3, 80, 40, [0.95, 0.995, 0.9995], _moe(2, 1, 72), rot_dims=32, base=77.0),
@@ -297,7 +298,7 @@ class RetentionCase:
 
 
 @pytest.mark.parametrize("heads,dim,vdim,rot_dims", [(3, 16, 24, 8), (2, 80, 40, 80), (1, 8, 136, 0),
-                                                    (2, 64, 64, 64)])
+                                                    (2, 64, 64, 64), (1, 160, 16, 32)])
 def test_retention_kernels(heads, dim, vdim, rot_dims):
     """A whole sequence at once, in portions down to one token, beside another request, in any
     split of the value columns over CTAs; a slot's earlier state is not read at position 0."""
