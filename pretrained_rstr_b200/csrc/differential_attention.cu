@@ -469,7 +469,7 @@ diff_attention_tile_kernel(O* __restrict__ out, long out_ld, const float* __rest
 // 32 keys w * 32 .. of the super-block for every pair, with a running state of its own, and the
 // warps' states are joined in warp order at the end.  The order of every sum depends on
 // absolute positions and nw only (nw: from the sizes alone).
-template <typename C, typename O>
+template <typename C, typename O, int VC>
 __global__ void __launch_bounds__(DT_WARPS * 32)
 diff_attention_single_kernel(O* __restrict__ out, long out_ld, const float* __restrict__ q,
                              const C* __restrict__ cache, const int* __restrict__ block_table,
@@ -504,14 +504,14 @@ diff_attention_single_kernel(O* __restrict__ out, long out_ld, const float* __re
     const int* table = block_table + (size_t)b * max_pages;
     for (int e = threadIdx.x; e < hg * 2 * dim; e += blockDim.x)
         Qs[e] = q[((size_t)t * heads + g * hg) * 2 * dim + e] * scale;
-    float acc1[DT_PPW][DT_VC], acc2[DT_PPW][DT_VC];
+    float acc1[DT_PPW][VC], acc2[DT_PPW][VC];
     float m1[DT_PPW], m2[DT_PPW], l1[DT_PPW], l2[DT_PPW];
 #pragma unroll
     for (int x = 0; x < DT_PPW; ++x) {
         m1[x] = m2[x] = -INFINITY;
         l1[x] = l2[x] = 0.0f;
 #pragma unroll
-        for (int c = 0; c < DT_VC; ++c) acc1[x][c] = acc2[x][c] = 0.0f;
+        for (int c = 0; c < VC; ++c) acc1[x][c] = acc2[x][c] = 0.0f;
     }
     for (int j0 = (lo / span) * span; j0 <= pos; j0 += span) {
         __syncthreads();
@@ -563,38 +563,71 @@ diff_attention_single_kernel(O* __restrict__ out, long out_ld, const float* __re
         const float* krow = Ks + (warp * DT_KB + lane) * kpitch;
         const float* vblk = Vs + (size_t)warp * DT_KB * vdim;
         const int k_hi = min(DT_KB, pos - jb + 1);
+        // scores of this lane's key for all pairs: the key's numbers are loaded once, a pair's
+        // query in 16-byte pieces
+        float s1[DT_PPW], s2[DT_PPW];
+#pragma unroll
+        for (int x = 0; x < DT_PPW; ++x) s1[x] = s2[x] = 0.0f;
+        if (dim % 4 == 0) {
+            for (int d = 0; d < dim; d += 4) {
+                const float a0 = krow[d], a1 = krow[d + 1], a2 = krow[d + 2], a3 = krow[d + 3];
+                const float b0 = krow[dim + d], b1 = krow[dim + d + 1], b2 = krow[dim + d + 2],
+                            b3 = krow[dim + d + 3];
+#pragma unroll
+                for (int x = 0; x < DT_PPW; ++x) {
+                    if (x < hg) {
+                        const float* qrow = Qs + x * 2 * dim;
+                        const float4 u = *reinterpret_cast<const float4*>(qrow + d);
+                        const float4 w = *reinterpret_cast<const float4*>(qrow + dim + d);
+                        s1[x] = fmaf(u.w, a3, fmaf(u.z, a2, fmaf(u.y, a1, fmaf(u.x, a0, s1[x]))));
+                        s2[x] = fmaf(w.w, b3, fmaf(w.z, b2, fmaf(w.y, b1, fmaf(w.x, b0, s2[x]))));
+                    }
+                }
+            }
+        } else {
+            for (int d = 0; d < dim; ++d) {
+                const float a0 = krow[d], b0 = krow[dim + d];
+#pragma unroll
+                for (int x = 0; x < DT_PPW; ++x) {
+                    if (x < hg) {
+                        s1[x] = fmaf(Qs[x * 2 * dim + d], a0, s1[x]);
+                        s2[x] = fmaf(Qs[x * 2 * dim + dim + d], b0, s2[x]);
+                    }
+                }
+            }
+        }
+        float e1[DT_PPW], e2[DT_PPW];
 #pragma unroll
         for (int x = 0; x < DT_PPW; ++x) {
-            if (x >= hg) break;
-            const float* qrow = Qs + x * 2 * dim;
-            float s1 = 0.0f, s2 = 0.0f;
-            for (int d = 0; d < dim; ++d) {
-                s1 = fmaf(qrow[d], krow[d], s1);
-                s2 = fmaf(qrow[dim + d], krow[dim + d], s2);
-            }
-            s1 = vis ? s1 : -INFINITY;
-            s2 = vis ? s2 : -INFINITY;
-            const float n1 = fmaxf(m1[x], prb_warp_max(s1)), n2 = fmaxf(m2[x], prb_warp_max(s2));
+            e1[x] = e2[x] = 0.0f;
+            if (x >= hg) continue;
+            const float t1 = vis ? s1[x] : -INFINITY, t2 = vis ? s2[x] : -INFINITY;
+            const float n1 = fmaxf(m1[x], prb_warp_max(t1)), n2 = fmaxf(m2[x], prb_warp_max(t2));
             const float f1 = expf(m1[x] - n1), f2 = expf(m2[x] - n2);
-            const float e1 = vis ? expf(s1 - n1) : 0.0f, e2 = vis ? expf(s2 - n2) : 0.0f;
-            l1[x] = l1[x] * f1 + prb_warp_sum(e1);
-            l2[x] = l2[x] * f2 + prb_warp_sum(e2);
+            e1[x] = vis ? expf(t1 - n1) : 0.0f;
+            e2[x] = vis ? expf(t2 - n2) : 0.0f;
+            l1[x] = l1[x] * f1 + prb_warp_sum(e1[x]);
+            l2[x] = l2[x] * f2 + prb_warp_sum(e2[x]);
             m1[x] = n1;
             m2[x] = n2;
 #pragma unroll
-            for (int c = 0; c < DT_VC; ++c) {
+            for (int c = 0; c < VC; ++c) {
                 acc1[x][c] *= f1;
                 acc2[x][c] *= f2;
             }
-            for (int kk = 0; kk < k_hi; ++kk) {
-                const float w1 = __shfl_sync(0xffffffffu, e1, kk), w2 = __shfl_sync(0xffffffffu, e2, kk);
+        }
+        for (int kk = 0; kk < k_hi; ++kk) {
+            float v[VC];
 #pragma unroll
-                for (int c = 0; c < DT_VC; ++c) {
-                    const int col = lane + 32 * c;
-                    if (col < vdim) {
-                        const float v = vblk[kk * vdim + col];
-                        acc1[x][c] = fmaf(w1, v, acc1[x][c]);
-                        acc2[x][c] = fmaf(w2, v, acc2[x][c]);
+            for (int c = 0; c < VC; ++c) v[c] = (lane + 32 * c < vdim) ? vblk[kk * vdim + lane + 32 * c] : 0.0f;
+#pragma unroll
+            for (int x = 0; x < DT_PPW; ++x) {
+                if (x < hg) {
+                    const float w1 = __shfl_sync(0xffffffffu, e1[x], kk), w2 = __shfl_sync(0xffffffffu, e2[x], kk);
+#pragma unroll
+                    for (int c = 0; c < VC; ++c) {
+                        acc1[x][c] = fmaf(w1, v[c], acc1[x][c]);
+                        acc2[x][c] = fmaf(w2, v[c], acc2[x][c]);
                     }
                 }
             }
@@ -612,7 +645,7 @@ diff_attention_single_kernel(O* __restrict__ out, long out_ld, const float* __re
             mine[0] = m1[x]; mine[1] = l1[x]; mine[2] = m2[x]; mine[3] = l2[x];
         }
 #pragma unroll
-        for (int c = 0; c < DT_VC; ++c)
+        for (int c = 0; c < VC; ++c)
             if (lane + 32 * c < vdim) {
                 mine[4 + lane + 32 * c] = acc1[x][c];
                 mine[4 + vdim + lane + 32 * c] = acc2[x][c];
@@ -627,9 +660,9 @@ diff_attention_single_kernel(O* __restrict__ out, long out_ld, const float* __re
             M1 = fmaxf(M1, rcd[0]);
             M2 = fmaxf(M2, rcd[2]);
         }
-        float L1 = 0.0f, L2 = 0.0f, a1[DT_VC], a2[DT_VC];
+        float L1 = 0.0f, L2 = 0.0f, a1[VC], a2[VC];
 #pragma unroll
-        for (int c = 0; c < DT_VC; ++c) a1[c] = a2[c] = 0.0f;
+        for (int c = 0; c < VC; ++c) a1[c] = a2[c] = 0.0f;
         for (int w = 0; w < nw; ++w) {
             const float* rcd = J + ((size_t)w * hg + x) * rec;
             const float f1 = rcd[0] == -INFINITY ? 0.0f : expf(rcd[0] - M1);
@@ -637,16 +670,16 @@ diff_attention_single_kernel(O* __restrict__ out, long out_ld, const float* __re
             L1 = fmaf(rcd[1], f1, L1);
             L2 = fmaf(rcd[3], f2, L2);
 #pragma unroll
-            for (int c = 0; c < DT_VC; ++c)
+            for (int c = 0; c < VC; ++c)
                 if (lane + 32 * c < vdim) {
                     a1[c] = fmaf(rcd[4 + lane + 32 * c], f1, a1[c]);
                     a2[c] = fmaf(rcd[4 + vdim + lane + 32 * c], f2, a2[c]);
                 }
         }
-        float o[DT_VC];
+        float o[VC];
         float ss = 0.0f;
 #pragma unroll
-        for (int c = 0; c < DT_VC; ++c) {
+        for (int c = 0; c < VC; ++c) {
             const float u1 = L1 > 0.0f ? a1[c] / L1 : 0.0f;
             const float u2 = L2 > 0.0f ? a2[c] / L2 : 0.0f;
             o[c] = (lane + 32 * c < vdim) ? u1 - lambda * u2 : 0.0f;
@@ -656,7 +689,7 @@ diff_attention_single_kernel(O* __restrict__ out, long out_ld, const float* __re
         const float inv = out_scale / sqrtf(ss / (float)vdim + eps);
         O* dst = out + (size_t)t * out_ld + (size_t)(g * hg + x) * vdim;
 #pragma unroll
-        for (int c = 0; c < DT_VC; ++c)
+        for (int c = 0; c < VC; ++c)
             if (lane + 32 * c < vdim) dst[lane + 32 * c] = prb_from_float<O>(o[c] * inv);
     }
 }
@@ -792,20 +825,30 @@ PRB_API int prb_diff_attention_single(void* out, long out_ld, const float* q, co
     const size_t join = (size_t)nw * hg * (4 + 2 * vdim) * sizeof(float);
     if (join > smem) smem = join;
     dim3 grid(n_tokens, kv_heads);
-#define DIFFS(CT, OT)                                                                            \
+#define DIFFS1(CT, OT, VCN)                                                                      \
     do {                                                                                         \
         if (smem > 48 * 1024)                                                                    \
-            cudaFuncSetAttribute(diff_attention_single_kernel<CT, OT>,                           \
+            cudaFuncSetAttribute(diff_attention_single_kernel<CT, OT, VCN>,                      \
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);        \
-        diff_attention_single_kernel<CT, OT><<<grid, nw * 32, smem, stream>>>(                   \
+        diff_attention_single_kernel<CT, OT, VCN><<<grid, nw * 32, smem, stream>>>(              \
             (OT*)out, out_ld, q, (const CT*)cache, block_table, seq_of_token, positions,         \
             n_tokens, heads, kv_heads, dim, vdim, page_size, max_pages, num_pages, block, scale, \
             lambda, eps, out_scale, status);                                                     \
+    } while (0)
+#define DIFFS(CT, OT)                                                                            \
+    do {                                                                                         \
+        switch ((vdim + 31) / 32) {                                                              \
+            case 1: DIFFS1(CT, OT, 1); break;                                                    \
+            case 2: DIFFS1(CT, OT, 2); break;                                                    \
+            case 3: DIFFS1(CT, OT, 3); break;                                                    \
+            default: DIFFS1(CT, OT, 4); break;                                                   \
+        }                                                                                        \
     } while (0)
     if (cache_dtype == PRB_F32 && out_dtype == PRB_F32) DIFFS(float, float);
     else if (cache_dtype == PRB_BF16 && out_dtype == PRB_BF16) DIFFS(__nv_bfloat16, __nv_bfloat16);
     else return PRB_E_DTYPE;
 #undef DIFFS
+#undef DIFFS1
     PRB_LAUNCH_CHECK();
     return 0;
 }

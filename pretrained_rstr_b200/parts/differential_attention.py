@@ -102,7 +102,9 @@ class DifferentialAttention(Mixer):
         # a step of single tokens: a CTA per (token, key/value head) whose warps share the keys;
         # portions of prompts: as many consecutive rows as the tiled kernel takes, which share
         # every key they stage
-        single = ctx.layout.t_cap <= ctx.layout.b_cap
+        # (both kernels take any step; a step replayed from a graph keeps the choice of the step
+        # that was recorded)
+        single = ctx.max_q_len == 1 or ctx.layout.t_cap <= ctx.layout.b_cap
         ops.diff_attention(o, q, cache.k, group.block_table, ctx.seq_of_token, ctx.positions,
                            self.heads, self.dim, self.vdim, self.block, self.scale, self.lam,
                            self.eps, self.out_scale, ctx.status,
