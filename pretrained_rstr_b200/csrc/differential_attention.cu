@@ -464,7 +464,8 @@ diff_attention_tile_kernel(O* __restrict__ out, long out_ld, const float* __rest
     }
 }
 // ------------------------------------------------------------ single tokens (decoding)
-// A CTA per (token, key/value head); its few (query head) pairs ride together.  Keys go in
+// A CTA per (token, key/value head) (several where more than four query heads share the
+// head); its few (query head) pairs ride together.  Keys go in
 // super-blocks of nw * 32 ABSOLUTE positions, staged at once by all warps; warp w then takes the
 // 32 keys w * 32 .. of the super-block for every pair, with a running state of its own, and the
 // warps' states are joined in warp order at the end.  The order of every sum depends on
@@ -481,8 +482,13 @@ diff_attention_single_kernel(O* __restrict__ out, long out_ld, const float* __re
     __shared__ int pages_s[DT_WARPS * DT_KB];
     prb_grid_launch_dependents();
     const int nw = blockDim.x >> 5;
-    const int hg = heads / kv_heads;                 // <= DT_PPW
-    const int g = blockIdx.y, t = blockIdx.x;
+    // (more than DT_PPW query heads a key/value head: several CTAs share the head, each with
+    // up to DT_PPW of its query heads)
+    const int per_kv = heads / kv_heads;
+    const int parts = (per_kv + DT_PPW - 1) / DT_PPW;
+    const int g = blockIdx.y / parts, part = blockIdx.y - g * parts, t = blockIdx.x;
+    const int h0 = g * per_kv + part * DT_PPW;       // first query head of this CTA
+    const int hg = min(DT_PPW, per_kv - part * DT_PPW);
     if (t >= n_tokens) return;
     const int rowlen = 2 * dim + vdim;
     const int kpitch = 2 * dim + 1;
@@ -497,13 +503,13 @@ diff_attention_single_kernel(O* __restrict__ out, long out_ld, const float* __re
         if (b >= 0 && threadIdx.x == 0)
             prb_set_status(status, PRB_S_POSITION_RANGE, t, pos, max_pages * page_size);
         for (int j = threadIdx.x; j < hg * vdim; j += blockDim.x)
-            out[(size_t)t * out_ld + (size_t)g * hg * vdim + j] = prb_from_float<O>(0.0f);
+            out[(size_t)t * out_ld + (size_t)h0 * vdim + j] = prb_from_float<O>(0.0f);
         return;
     }
     const int lo = block > 0 ? (pos / block) * block : 0;
     const int* table = block_table + (size_t)b * max_pages;
     for (int e = threadIdx.x; e < hg * 2 * dim; e += blockDim.x)
-        Qs[e] = q[((size_t)t * heads + g * hg) * 2 * dim + e] * scale;
+        Qs[e] = q[((size_t)t * heads + h0) * 2 * dim + e] * scale;
     float acc1[DT_PPW][VC], acc2[DT_PPW][VC];
     float m1[DT_PPW], m2[DT_PPW], l1[DT_PPW], l2[DT_PPW];
 #pragma unroll
@@ -652,8 +658,7 @@ diff_attention_single_kernel(O* __restrict__ out, long out_ld, const float* __re
             }
     }
     __syncthreads();
-    if (warp < hg) {
-        const int x = warp;
+    for (int x = warp; x < hg; x += nw) {            // a pair a warp
         float M1 = -INFINITY, M2 = -INFINITY;
         for (int w = 0; w < nw; ++w) {
             const float* rcd = J + ((size_t)w * hg + x) * rec;
@@ -687,7 +692,7 @@ diff_attention_single_kernel(O* __restrict__ out, long out_ld, const float* __re
         }
         ss = prb_warp_sum(ss);
         const float inv = out_scale / sqrtf(ss / (float)vdim + eps);
-        O* dst = out + (size_t)t * out_ld + (size_t)(g * hg + x) * vdim;
+        O* dst = out + (size_t)t * out_ld + (size_t)(h0 + x) * vdim;
 #pragma unroll
         for (int c = 0; c < VC; ++c)
             if (lane + 32 * c < vdim) dst[lane + 32 * c] = prb_from_float<O>(o[c] * inv);
@@ -800,14 +805,13 @@ PRB_API int prb_diff_attention_tile(void* out, long out_ld, const float* q, cons
 // Warps of the single-token kernel for these sizes (0: it does not take them).
 PRB_API int prb_diff_attention_single_warps(int heads, int kv_heads, int dim, int vdim) {
     if (heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0) return 0;
-    const int hg = heads / kv_heads;
-    if (hg > DT_PPW || vdim > 32 * DT_VC || dim > 256) return 0;
+    const int hg = heads / kv_heads < DT_PPW ? heads / kv_heads : DT_PPW;
+    if (vdim > 32 * DT_VC || dim > 256) return 0;
     const size_t fixed = (size_t)hg * 2 * dim * sizeof(float);
     const size_t per_warp = (size_t)DT_KB * (2 * dim + 1 + vdim) * sizeof(float);
     int nw = (int)((180 * 1024 - fixed) / per_warp);
     if (nw > DT_WARPS) nw = DT_WARPS;
-    if (nw < hg) return 0;                           // (the join gives a pair to a warp)
-    return nw;
+    return nw < 1 ? 0 : nw;
 }
 
 PRB_API int prb_diff_attention_single(void* out, long out_ld, const float* q, const void* cache,
@@ -820,11 +824,14 @@ PRB_API int prb_diff_attention_single(void* out, long out_ld, const float* q, co
     if (n_tokens <= 0) return 0;
     const int nw = prb_diff_attention_single_warps(heads, kv_heads, dim, vdim);
     if (nw <= 0 || kv_heads > 65535 || page_size <= 0 || max_pages <= 0 || block < 0) return PRB_E_SIZE;
-    const int hg = heads / kv_heads;
+    const int per_kv = heads / kv_heads;
+    const int hg = per_kv < DT_PPW ? per_kv : DT_PPW;
+    const int parts = (per_kv + DT_PPW - 1) / DT_PPW;
+    if ((long)kv_heads * parts > 65535) return PRB_E_SIZE;
     size_t smem = (size_t)(nw * DT_KB * (2 * dim + 1 + vdim) + hg * 2 * dim) * sizeof(float);
     const size_t join = (size_t)nw * hg * (4 + 2 * vdim) * sizeof(float);
     if (join > smem) smem = join;
-    dim3 grid(n_tokens, kv_heads);
+    dim3 grid(n_tokens, kv_heads * parts);
 #define DIFFS1(CT, OT, VCN)                                                                      \
     do {                                                                                         \
         if (smem > 48 * 1024)                                                                    \

@@ -1385,8 +1385,8 @@ def diff_attention_tile_rows(heads: int, kv_heads: int, dim: int, vdim: int) -> 
 
 
 def diff_attention_single_warps(heads: int, kv_heads: int, dim: int, vdim: int) -> int:
-    """Warps of the single-token kernel at these sizes; 0: it does not take them (more than
-    four query heads a key head, value heads wider than 128)."""
+    """Warps of the single-token kernel at these sizes; 0: it does not take them (value heads
+    wider than 128)."""
     return int(lib().prb_diff_attention_single_warps(heads, kv_heads, dim, vdim))
 
 

@@ -157,9 +157,10 @@ __global__ void routed_act1_kernel(O* __restrict__ out, long out_ld, const float
     out[(size_t)t * out_ld + i] = prb_from_float<O>(v);
 }
 // ------------------------------------------------- router and activation in one launch
-// A CTA per token: the scores of the token's router logits (columns of the same 32-bit
-// product that holds the experts' first results), the choice, then the activation of the row
-// with the chosen experts' weights (the others' columns come out zero and are not read).
+// CTAs (token, slice of the row's columns): the scores of the token's router logits (columns of
+// the same 32-bit product that holds the experts' first results) and the choice, by every CTA
+// of the token for itself, then the activation of the CTA's columns with the chosen experts'
+// weights (the others' columns come out zero and are not read).
 template <typename O>
 __global__ void route_act_kernel(O* __restrict__ out, long out_ld, const float* __restrict__ in,
                                  long in_ld, int in_col, int router_col, int n_rows, int n_experts,
@@ -196,14 +197,17 @@ __global__ void route_act_kernel(O* __restrict__ out, long out_ld, const float* 
             for (int e = 0; e < n_experts; ++e) wt[e] /= sum;
     }
     __syncthreads();
-    if (weights_out)
+    if (weights_out && blockIdx.y == 0)
         for (int e = threadIdx.x; e < n_experts; e += blockDim.x) weights_out[(size_t)t * n_experts + e] = wt[e];
-    const int n = n_experts * group;
+    const int n_all = n_experts * group;
+    const int per_cta = (n_all + gridDim.y - 1) / gridDim.y;
+    const int c_lo = ((blockIdx.y * per_cta + 3) / 4) * 4;              // slices start at multiples of 4
+    const int n = min(n_all, (((blockIdx.y + 1) * per_cta + 3) / 4) * 4);
     O* o = out + (size_t)t * out_ld;
     const bool vec = group % 4 == 0 && in_col % 4 == 0 && in_ld % 4 == 0 && out_ld % 4 == 0 &&
                      ((uintptr_t)in) % 16 == 0 && ((uintptr_t)out) % (4 * sizeof(O)) == 0;
     if (vec) {
-        for (int i = threadIdx.x * 4; i < n; i += blockDim.x * 4) {
+        for (int i = c_lo + threadIdx.x * 4; i < n; i += blockDim.x * 4) {
             const float wgt = wt[i / group];
             float v[4] = {0.0f, 0.0f, 0.0f, 0.0f};
             if (wgt != 0.0f) {
@@ -225,7 +229,7 @@ __global__ void route_act_kernel(O* __restrict__ out, long out_ld, const float* 
             }
         }
     } else {
-        for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        for (int i = c_lo + threadIdx.x; i < n; i += blockDim.x) {
             const float wgt = wt[i / group];
             float v = 0.0f;
             if (wgt != 0.0f) {
@@ -322,12 +326,17 @@ PRB_API int prb_route_act(void* out, long out_ld, const float* in, long in_ld, i
         return PRB_E_SIZE;
     if (score_fn < 0 || score_fn > 1 || act < 0 || act > 3) return PRB_E_ARG;
     const size_t smem = (size_t)2 * n_experts * sizeof(float);
+    // slices of 4,096 columns, fewer while the rows alone fill the GPU
+    int slices = (n_experts * group + 4095) / 4096;
+    if (slices > 64) slices = 64;
+    while (slices > 1 && (long)n_rows * slices > 8L * prb_sm_count()) slices = (slices + 1) / 2;
+    const dim3 grid(n_rows, slices);
     if (out_dtype == PRB_F32)
-        route_act_kernel<float><<<n_rows, 256, smem, stream>>>(
+        route_act_kernel<float><<<grid, 256, smem, stream>>>(
             (float*)out, out_ld, in, in_ld, in_col, router_col, n_rows, n_experts, top, score_fn,
             renorm, group, act, on_output, weights_out);
     else if (out_dtype == PRB_BF16)
-        route_act_kernel<__nv_bfloat16><<<n_rows, 256, smem, stream>>>(
+        route_act_kernel<__nv_bfloat16><<<grid, 256, smem, stream>>>(
             (__nv_bfloat16*)out, out_ld, in, in_ld, in_col, router_col, n_rows, n_experts, top,
             score_fn, renorm, group, act, on_output, weights_out);
     else

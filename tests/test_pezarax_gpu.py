@@ -47,7 +47,7 @@ def _model(vocab, width, layers, loop=None, scale=5.0, logit_scale=1.0, eps=1e-6
 # cover a part, all or nothing of a head; blocks shorter and longer than a page and than the
 # kernel's key segment; a loop in the middle, a loop from the first layer on, no loop; a model
 # without attention (no pages at all) and one whose first layer is attention; two, three and
-# eight query heads a key/value head (eight: more than the single-token kernel takes).
+# eight query heads a key/value head (eight: two CTAs of the single-token kernel a head).
 SHAPE_A = _model(300, 64, [
     _ret(2, 16, 24, [0.9, 0.99], _moe(5, 2, 24), rot_dims=8),
     _att(4, 2, 16, 24, 20, _moe(3, 1, 40), rot_dims=12, diff=0.25),
