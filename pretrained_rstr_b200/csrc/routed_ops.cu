@@ -42,8 +42,8 @@ __global__ void embed_scaled_kernel(float* __restrict__ out, float* __restrict__
 
 // ------------------------------------------------------------------ router by scores
 // z[e] = x . w[e] (32-bit accumulation; x in X), or, with w == null, x[t, e] holds z already.
-// score_fn 0: s = sigmoid(z); 1: s = z.  The `top` largest s are chosen (ties: the lower
-// index).  weights[t, e] = s[e] at chosen experts (divided by the chosen scores' sum when
+// score_fn 0: s = sigmoid(z); 1: s = z.  The `top` largest s are chosen, by their z (the same
+// order, and large logits whose sigmoids all round to 1 still differ; ties: the lower index).  weights[t, e] = s[e] at chosen experts (divided by the chosen scores' sum when
 // `renorm`), zero elsewhere; chosen / chosen_w list them by rank.
 template <typename X, typename W>
 __global__ void route_scores_kernel(float* __restrict__ weights, int* __restrict__ chosen,
@@ -58,8 +58,7 @@ __global__ void route_scores_kernel(float* __restrict__ weights, int* __restrict
     const X* xr = x + (size_t)t * x_ld;
     if (w == nullptr) {
         for (int e = threadIdx.x; e < n_experts; e += blockDim.x) {
-            const float z = prb_to_float<X>(xr[e]);
-            s[e] = score_fn == 0 ? sigmoidf_(z) : z;
+            s[e] = prb_to_float<X>(xr[e]);
         }
     } else {
         for (int e = warp; e < n_experts; e += nwarps) {
@@ -68,7 +67,7 @@ __global__ void route_scores_kernel(float* __restrict__ weights, int* __restrict
             for (int i = lane; i < width; i += 32)
                 acc = fmaf(prb_to_float<X>(xr[i]), prb_to_float<W>(we[i]), acc);
             acc = prb_warp_sum(acc);
-            if (lane == 0) s[e] = score_fn == 0 ? sigmoidf_(acc) : acc;
+            if (lane == 0) s[e] = acc;
         }
     }
     for (int e = threadIdx.x; e < n_experts; e += blockDim.x) weights[(size_t)t * n_experts + e] = 0.0f;
@@ -83,9 +82,10 @@ __global__ void route_scores_kernel(float* __restrict__ weights, int* __restrict
                 if (v == v && (arg < 0 || v > best)) { best = v; arg = e; }
             }
             if (arg < 0) arg = k;               // (a row of NaNs: padding, or a fault upstream)
+            const float score = score_fn == 0 ? sigmoidf_(best) : best;
             chosen[(size_t)t * top + k] = arg;
-            chosen_w[(size_t)t * top + k] = best;
-            sum += best;
+            chosen_w[(size_t)t * top + k] = score;
+            sum += score;
             s[arg] = NAN;                       // taken
         }
         for (int k = 0; k < top; ++k) {
@@ -174,8 +174,7 @@ __global__ void route_act_kernel(O* __restrict__ out, long out_ld, const float* 
     if (t >= n_rows) return;
     const float* row = in + (size_t)t * in_ld;
     for (int e = threadIdx.x; e < n_experts; e += blockDim.x) {
-        const float z = row[router_col + e];
-        sc[e] = score_fn == 0 ? sigmoidf_(z) : z;
+        sc[e] = row[router_col + e];             // chosen by the logits: see route_scores
         wt[e] = 0.0f;
     }
     __syncthreads();
@@ -189,8 +188,9 @@ __global__ void route_act_kernel(O* __restrict__ out, long out_ld, const float* 
                 if (v == v && (arg < 0 || v > best)) { best = v; arg = e; }
             }
             if (arg < 0) break;                  // (a row of NaNs: padding, or a fault upstream)
-            wt[arg] = best;
-            sum += best;
+            const float score = score_fn == 0 ? sigmoidf_(best) : best;
+            wt[arg] = score;
+            sum += score;
             sc[arg] = NAN;                       // taken
         }
         if (renorm)

@@ -189,6 +189,14 @@ def test_router_and_expert_activation_kernels():
         ops.route_scores(weights, chosen, chosen_w, logits.to(DEV)[:, 3:3 + n_e], None, top,
                          renormalize=True)
         assert torch.allclose(chosen_w.cpu(), val / val.sum(-1, keepdim=True), atol=1e-6)
+    # logits so large that their sigmoids all round to 1: the order of the logits decides
+    big = torch.tensor([[40.0, 45.0, 30.0, -3.0, 44.0, 20.0]], device=DEV)
+    w1, c1, cw1 = torch.empty(1, 6, device=DEV), torch.empty(1, 2, dtype=torch.int32, device=DEV), torch.empty(1, 2, device=DEV)
+    ops.route_scores(w1, c1, cw1, big, None, 2)
+    assert c1.cpu().tolist() == [[1, 4]] and cw1.cpu().tolist() == [[1.0, 1.0]]
+    act = torch.zeros(1, 16, device=DEV)
+    ops.route_act(act, torch.cat([torch.ones(1, 12, device=DEV), big], dim=1), 0, 12, 6, 2, 2, weights_out=w1)
+    assert w1.cpu().tolist() == [[0.0, 1.0, 0.0, 0.0, 1.0, 0.0]]
     for xt in (torch.float32, torch.bfloat16):                   # the router's own product
         x, w = torch.randn(t, 32, generator=g).to(xt), torch.randn(n_e, 32, generator=g).to(xt)
         ops.route_scores(weights, chosen, chosen_w, x.to(DEV), w.to(DEV), 6, score="identity")
